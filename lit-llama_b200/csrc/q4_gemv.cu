@@ -11,7 +11,7 @@
 //     scaled by a power of two 2^sh chosen from max|x| and rounded to X[k] (|X| < 2^22: 14 bits of dynamic range
 //     below the largest element before an 8-bit significand loses a bit, and a rounding unit of 2^-22 max|x| from
 //     there on), then split into three balanced base-256 digits X = sum_j d_j 256^j, d_j in [-128, 127];
-//   * mma.sync.m16n8k32 (u8 x s8 -> s32, SASS IMMA.16832.U8.S8) has 8 result columns and a single activation row
+//   * mma.sync.m16n8k32 (u8 x s8 -> s32) has 8 result columns and a single activation row
 //     needs one: digit plane j is column j, so all digits cost ONE MMA per 16 x 32 weight tile;
 //   * a packed byte holds two levels.  It is fed to the tensor core UNMASKED as the operand of row g (value
 //     level[g] + 16 level[g+8]) and with the low nibbles masked off as the operand of row g + 8 (16 level[g+8]):

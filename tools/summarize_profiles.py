@@ -46,7 +46,7 @@ def full(tag, rep, name, title):
     raw = subprocess.run(["ncu", "-i", os.path.join(G, rep), "--page", "raw", "--csv"], capture_output=True, text=True).stdout
     rows = list(csv.reader(raw.splitlines()))
     h, units = rows[0], rows[1]
-    lines = [f"# {title}", "# ncu --set full --clock-control none --import-source on  (one launch at a time, cold cache, no PDL overlap;",
+    lines = [f"# {title}", "# ncu --set full --clock-control none  (one launch at a time, cold cache, no PDL overlap;",
              "# durations here are NOT bench numbers - bench.py times the kernels with CUDA events inside the pipelined step)"]
     for r in rows[2:]:
         lines.append("")
