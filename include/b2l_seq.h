@@ -1,0 +1,129 @@
+/*
+ * b2l_seq.h - C ABI of libb200seq.so: sequence-mixer kernels for B200 (sm_100a) beside the quantized-LLaMA
+ * library (b2l.h).  One call = one mechanism over one portion of ONE sequence: T consecutive tokens that start at
+ * position pos0 of the sequence held in state slot `slot`.
+ *
+ * Conventions (those of b2l.h unless stated):
+ *  - every pointer is a device pointer owned by the caller; calls only enqueue on `stream` (graph capturable);
+ *    0 = ok, <0 = B2L_E_*, >0 = cudaError_t; b2l_seq_last_error() gives the message; no CPU fallback.
+ *  - `meta` is a device int32[2] = {slot, pos0}: kernels read it on the device, so a captured decode step replays
+ *    for any slot and position.
+ *  - "act" tensors (projection outputs, weights, caches) have the dtype `act_dtype` (B2L_BF16 or B2L_F32);
+ *    everything named f32 is float.  What a recurrence or a softmax consumes is f32 in both modes: residual,
+ *    norms, angles, scores, decays, gates of a recurrence, states.
+ *  - row-major, leading dimensions in elements; a "heads x size" operand is `heads` consecutive blocks of `size`.
+ */
+#ifndef B2L_SEQ_H_
+#define B2L_SEQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "b2l.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int b2l_seq_version(void);
+const char* b2l_seq_last_error(void);
+
+/* x[t, :] = table[token[t], :] * scale (f32 residual stream).  Tokens outside the table read row 0. */
+int b2l_seq_embed(const void* tokens, int tokens_i64, const void* table, int act_dtype, float scale, float* x,
+                  int T, int D, int vocab, b2l_stream_t stream);
+
+/* out[t, :] = x / sqrt(mean(x^2) + eps) * w, x f32 -> out act.  `rows` (device int32[n_rows], may be null) picks
+ * the rows of x to normalise (out row r <- x row rows[r]); null = rows 0..n_rows-1. */
+int b2l_seq_rmsnorm(const float* x, const void* w, float eps, void* out, const int* rows, int n_rows, int D,
+                    int act_dtype, b2l_stream_t stream);
+
+/* Post-norm residual step fused with the next pre-norm:
+ *   x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w_post;   if w_next: h[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w_next */
+int b2l_seq_norm_add_norm(const void* y, const void* w_post, float eps, float* x, const void* w_next, void* h, int T,
+                          int D, int act_dtype, b2l_stream_t stream);
+
+/* out[t, j] = act(gu[t, j]) * gu[t, F + j]  (gated feed-forward, both halves from one product). */
+enum { B2L_SEQ_ACT_GELU_TANH = 0, B2L_SEQ_ACT_SILU = 1, B2L_SEQ_ACT_SIGMOID = 2 };
+int b2l_seq_gated_act(const void* gu, int ldgu, void* out, int T, int F, int act, int act_dtype, b2l_stream_t stream);
+
+/* Short causal convolution over time per channel, then silu, with the last taps-1 inputs of the sequence carried
+ * in `state` ([n_slots][taps-1][C] act, oldest first; a fresh slot holds zeros):
+ *   out[t, c] = silu(bias[c] + sum_j w[c, taps-1-j] * in[t-j, c]),  in[<0] from the state.
+ * The state is advanced by the T tokens.  w is [C, taps] act, bias act or null, out f32. */
+int b2l_seq_conv_silu(const void* in, int ldin, const void* w, const void* bias, void* state, const int* meta,
+                      float* out, int ldout, int T, int C, int taps, int act_dtype, b2l_stream_t stream);
+
+/* In place on f32: every block of `size` becomes x * mult / sqrt(sum(x^2) + eps). */
+int b2l_seq_unit_norm(float* x, int ld, int T, int heads, int size, float eps, float mult, b2l_stream_t stream);
+
+/* Decay factors of a recurrence from a projection `a` (act, [T, lda], heads x size):
+ *   B2L_SEQ_DECAY_EXP_SOFTPLUS: dt = softplus(a + bias), out = exp(-exp(A_log[head]) * dt); dt_out (may be null)
+ *                               receives dt
+ *   B2L_SEQ_DECAY_SIGMOID_ROOT: out = sigmoid(a + bias)^(1/tau)
+ * bias is act [heads*size] (may be null), A_log act [heads]. */
+enum { B2L_SEQ_DECAY_EXP_SOFTPLUS = 0, B2L_SEQ_DECAY_SIGMOID_ROOT = 1 };
+int b2l_seq_decay(const void* a, int lda, const void* bias, const void* A_log, int mode, float tau, float* out,
+                  float* dt_out, int T, int heads, int size, int act_dtype, b2l_stream_t stream);
+
+/* Linear recurrence with a matrix state per head, S [K x V], carried per slot in f32:
+ *     S <- diag(d_t) S                           (d_t per key channel, or one number per head)
+ *     delta == 0:  S <- S + k_t v'_t^T
+ *     delta != 0:  u = sigmoid(beta_t) (v'_t - S^T k_t);  S <- S + k_t u^T
+ *     o_t = S^T q_t (+ skip[head] * v_t)
+ * with v'_t = v_t * vscale[t, head] when vscale is given.  q and k have `qk_heads` heads, value head h reads
+ * q/k head h / (heads / qk_heads).  `state` is [n_slots][heads][V][K] f32 (key channel fastest). */
+typedef struct {
+  const void* q; int ldq;                   /* f32, or act when qkv_act != 0 */
+  const void* k; int ldk;
+  const void* v; int ldv;
+  int qkv_act; float q_mult;                /* q is multiplied by q_mult when it is read */
+  const float* decay; int ldd; int decay_per_channel;
+  const void* beta; int ldb; int delta;     /* act [T, ldb], one per head; read only when delta != 0 */
+  const float* vscale; int ldvs;            /* f32 [T, heads] or null */
+  const void* skip;                         /* act [heads] or null */
+  float* state; const int* meta;
+  float* out; int ldo;
+  int T, heads, qk_heads, K, V, act_dtype;
+} b2l_seq_scan_args;
+int b2l_seq_scan(const b2l_seq_scan_args* a, b2l_stream_t stream);
+
+/* Read-out of a recurrence: groups of `group` consecutive channels of o (f32 [T, n]) are divided by their root
+ * mean square, multiplied by w (act; `w_shared` != 0: w has `group` entries used by every group, else n) and by
+ * act(gate) (act [T, ldg]) and by out_mult; gate_first != 0 applies the gate before the norm. */
+int b2l_seq_group_norm_gate(const float* o, int ldo, const void* w, int w_shared, const void* gate, int ldg,
+                            int gate_act, int gate_first, float eps, float out_mult, void* out, int ldout, int T,
+                            int n, int group, int act_dtype, b2l_stream_t stream);
+
+/* Per-head RMS norm (weight of `size`, shared by heads) then rotation of the first rot_dims entries of each head
+ * (entry i with entry i + rot_dims/2) by the angle (pos0 + t) * freq[i], cos and sin multiplied by rot_mult.
+ * x act [T, ldx] -> out act or f32 [T, heads*size] (out_f32).  w may be null (no norm), rot_dims may be 0. */
+int b2l_seq_headnorm_rope(const void* x, int ldx, const void* w, float eps, const float* freq, int rot_dims,
+                          float rot_mult, const int* meta, void* out, int out_f32, int T, int heads, int size,
+                          int act_dtype, b2l_stream_t stream);
+
+/* Block-local causal softmax attention with a sink: query at position p sees the keys j <= p with
+ * j / block == p / block; score s = softcap * tanh(q.k * scale / softcap) (softcap <= 0: none); weights
+ * exp(s_j) / (sink + sum exp(s_j)) with sink = 1 (has_sink) or 0; head h's output is multiplied by
+ * sigmoid(gate[t, h]) when gate is given.  Keys of this portion come from k_new / v_new, older ones of the same
+ * block from the ring cache ([n_slots][block][kv_heads][K or V] act, entry p % block).  After the call the ring
+ * holds the portion's tokens that share the last token's block. */
+typedef struct {
+  const float* q;                 /* f32 [T, heads*K], normalised and rotated */
+  const void* k_new;              /* act [T, kv_heads*K], normalised and rotated */
+  const void* v_new; int ldv;     /* act [T, ldv] */
+  void* cache_k; void* cache_v;
+  const int* meta;
+  const void* gate; int ldg;      /* act [T, ldg] or null */
+  void* out; int ldo;             /* act [T, ldo] */
+  float scale, softcap, out_mult;  /* out_mult scales the output (a mixing weight of a parallel branch) */
+  int has_sink, block, T, heads, kv_heads, K, V, act_dtype;
+} b2l_seq_attn_args;
+int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t stream);
+
+/* Zero one slot of a state tensor laid out [n_slots][slot_bytes]. */
+int b2l_seq_zero_slot(void* state, size_t slot_bytes, int slot, b2l_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2L_SEQ_H_ */

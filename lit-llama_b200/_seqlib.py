@@ -1,0 +1,115 @@
+"""ctypes binding of libb200seq.so (include/b2l_seq.h): the sequence-mixer kernels.  The library is compiled on
+first use when it is missing (only this library, not the quantized-LLaMA one).  No CPU or PyTorch fallback."""
+import ctypes as C
+import threading
+
+import torch
+
+from . import _build
+
+B2L_BF16, B2L_F32 = 0, 1
+ACT_GELU_TANH, ACT_SILU, ACT_SIGMOID = 0, 1, 2
+DECAY_EXP_SOFTPLUS, DECAY_SIGMOID_ROOT = 0, 1
+
+c_void_p, c_int, c_float, c_size_t = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+
+
+class ScanArgs(C.Structure):
+    _fields_ = [
+        ("q", c_void_p), ("ldq", c_int),
+        ("k", c_void_p), ("ldk", c_int),
+        ("v", c_void_p), ("ldv", c_int),
+        ("qkv_act", c_int), ("q_mult", c_float),
+        ("decay", c_void_p), ("ldd", c_int), ("decay_per_channel", c_int),
+        ("beta", c_void_p), ("ldb", c_int), ("delta", c_int),
+        ("vscale", c_void_p), ("ldvs", c_int),
+        ("skip", c_void_p),
+        ("state", c_void_p), ("meta", c_void_p),
+        ("out", c_void_p), ("ldo", c_int),
+        ("T", c_int), ("heads", c_int), ("qk_heads", c_int), ("K", c_int), ("V", c_int), ("act_dtype", c_int),
+    ]
+
+
+class AttnArgs(C.Structure):
+    _fields_ = [
+        ("q", c_void_p),
+        ("k_new", c_void_p),
+        ("v_new", c_void_p), ("ldv", c_int),
+        ("cache_k", c_void_p), ("cache_v", c_void_p),
+        ("meta", c_void_p),
+        ("gate", c_void_p), ("ldg", c_int),
+        ("out", c_void_p), ("ldo", c_int),
+        ("scale", c_float), ("softcap", c_float), ("out_mult", c_float),
+        ("has_sink", c_int), ("block", c_int), ("T", c_int), ("heads", c_int), ("kv_heads", c_int), ("K", c_int), ("V", c_int),
+        ("act_dtype", c_int),
+    ]
+
+
+_SIGS = {
+    "b2l_seq_version": (c_int, []),
+    "b2l_seq_last_error": (C.c_char_p, []),
+    "b2l_seq_embed": (c_int, [c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_rmsnorm": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_norm_add_norm": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_gated_act": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_conv_silu": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                  c_void_p]),
+    "b2l_seq_unit_norm": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p]),
+    "b2l_seq_decay": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                              c_void_p]),
+    "b2l_seq_scan": (c_int, [C.POINTER(ScanArgs), c_void_p]),
+    "b2l_seq_group_norm_gate": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p,
+                                        c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_headnorm_rope": (c_int, [c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_int,
+                                      c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_block_attention": (c_int, [C.POINTER(AttnArgs), c_void_p]),
+    "b2l_seq_zero_slot": (c_int, [c_void_p, c_size_t, c_int, c_void_p]),
+}
+
+EXPORTS = tuple(_SIGS)
+LIB_PATH = _build.LIBRARIES["seq"]["out"]
+
+_lib = None
+_lock = threading.Lock()
+
+
+def lib():
+    """The loaded library; built first (nvcc, sm_100a) when it is missing or older than its sources."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                handle = C.CDLL(_build.ensure("seq"))
+                for name, (res, args) in _SIGS.items():
+                    fn = getattr(handle, name)
+                    fn.restype = res
+                    fn.argtypes = args
+                _lib = handle
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = lib().b2l_seq_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"{what} failed (rc={rc}): {msg}")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def act_code(dtype: torch.dtype) -> int:
+    if dtype == torch.bfloat16:
+        return B2L_BF16
+    if dtype == torch.float32:
+        return B2L_F32
+    raise RuntimeError(f"dtype {dtype} unsupported: the sequence kernels take torch.bfloat16 or torch.float32")
+
+
+def ptr(t) -> int:
+    """Device pointer of a CUDA tensor (None -> null)."""
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise RuntimeError(f"tensor on {t.device}: the sequence kernels run on CUDA only (no CPU fallback)")
+    return t.data_ptr()

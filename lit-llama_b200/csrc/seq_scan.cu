@@ -1,0 +1,171 @@
+// Linear recurrences with a matrix state per head (gated delta rule, gated linear attention, state-space duality)
+// as ONE kernel: S <- diag(d) S; [u = sigmoid(beta)(v - S^T k)]; S <- S + k u^T; o = S^T q.
+//
+// A CTA owns one head and a tile of value columns; a column of S (K numbers) lives in the registers of R adjacent
+// lanes (SCAN_KPT numbers each), so a step is R-lane shuffles and no shared-memory traffic for S.  The state is
+// read once, carried through all T tokens of the portion and written once ([V][K] per head, K fastest, so the R
+// lanes of a column read consecutive 16-byte words).  Inputs of SCAN_TC steps are staged in shared memory by the
+// whole CTA.  All arithmetic is f32.
+#include "seq_common.cuh"
+
+namespace b2l {
+
+constexpr int SCAN_KPT = 16;       // state numbers per lane
+constexpr int SCAN_TC = 16;        // steps per shared-memory stage
+constexpr int SCAN_THREADS = 128;
+
+template <typename act_t>
+__device__ __forceinline__ float ld_in(const void* p, int is_act, size_t i) {
+  return is_act ? ld_act((const act_t*)p, i) : ((const float*)p)[i];
+}
+
+template <int DELTA, typename act_t>
+__global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_args a, int R) {
+  extern __shared__ float smem[];
+  const int KP = R * SCAN_KPT;                 // padded key size
+  const int cols = SCAN_THREADS / R;           // value columns of this CTA
+  const int DP = a.decay_per_channel ? KP : 1;
+  float* sq = smem;                            // [TC][KP]
+  float* sk = sq + SCAN_TC * KP;               // [TC][KP]
+  float* sd = sk + SCAN_TC * KP;               // [TC][DP]
+  float* sv = sd + SCAN_TC * DP;               // [TC][cols]  v' (scaled)
+  float* sraw = sv + SCAN_TC * cols;           // [TC][cols]  v as given (skip term)
+  float* so = sraw + SCAN_TC * cols;           // [TC][cols]
+  float* sb = so + SCAN_TC * cols;             // [TC] sigmoid(beta)
+
+  const int tid = threadIdx.x, r = tid % R, cidx = tid / R;
+  const int h = blockIdx.y, hq = h / (a.heads / a.qk_heads);
+  const int v0 = blockIdx.x * cols, vcol = v0 + cidx;
+  const int K = a.K, V = a.V;
+  const int slot = a.meta[0];
+  float* st = a.state + ((size_t)slot * a.heads + h) * (size_t)V * K;
+  const float skip = a.skip ? ld_act((const act_t*)a.skip, h) : 0.f;
+
+  float S[SCAN_KPT];
+#pragma unroll
+  for (int i = 0; i < SCAN_KPT; ++i) {
+    const int kk = ((i >> 2) * R + r) * 4 + (i & 3);
+    S[i] = (kk < K && vcol < V) ? st[(size_t)vcol * K + kk] : 0.f;
+  }
+
+  for (int t0 = 0; t0 < a.T; t0 += SCAN_TC) {
+    const int nt = min(SCAN_TC, a.T - t0);
+    __syncthreads();   // the previous stage's so[] has been written out
+    for (int i = tid; i < nt * KP; i += SCAN_THREADS) {
+      const int t = i / KP, kk = i % KP;
+      const bool in = kk < K;
+      sq[i] = in ? ld_in<act_t>(a.q, a.qkv_act, (size_t)(t0 + t) * a.ldq + (size_t)hq * K + kk) * a.q_mult : 0.f;
+      sk[i] = in ? ld_in<act_t>(a.k, a.qkv_act, (size_t)(t0 + t) * a.ldk + (size_t)hq * K + kk) : 0.f;
+      if (a.decay_per_channel) sd[i] = in ? a.decay[(size_t)(t0 + t) * a.ldd + (size_t)h * K + kk] : 1.f;
+    }
+    for (int i = tid; i < nt * cols; i += SCAN_THREADS) {
+      const int t = i / cols, c = i % cols;
+      float v = 0.f;
+      if (v0 + c < V) v = ld_in<act_t>(a.v, a.qkv_act, (size_t)(t0 + t) * a.ldv + (size_t)h * V + v0 + c);
+      sraw[i] = v;
+      sv[i] = a.vscale ? v * a.vscale[(size_t)(t0 + t) * a.ldvs + h] : v;
+    }
+    if (tid < nt) {
+      if (!a.decay_per_channel) sd[tid] = a.decay[(size_t)(t0 + tid) * a.ldd + h];
+      if (DELTA) sb[tid] = sigmoid_f(ld_act((const act_t*)a.beta, (size_t)(t0 + tid) * a.ldb + h));
+    }
+    __syncthreads();
+
+    for (int t = 0; t < nt; ++t) {
+      const float4* q4 = reinterpret_cast<const float4*>(sq + t * KP);
+      const float4* k4 = reinterpret_cast<const float4*>(sk + t * KP);
+      float kr[SCAN_KPT], qr[SCAN_KPT];
+#pragma unroll
+      for (int i4 = 0; i4 < SCAN_KPT / 4; ++i4) {
+        const float4 kv = k4[i4 * R + r], qv = q4[i4 * R + r];
+        kr[i4 * 4 + 0] = kv.x; kr[i4 * 4 + 1] = kv.y; kr[i4 * 4 + 2] = kv.z; kr[i4 * 4 + 3] = kv.w;
+        qr[i4 * 4 + 0] = qv.x; qr[i4 * 4 + 1] = qv.y; qr[i4 * 4 + 2] = qv.z; qr[i4 * 4 + 3] = qv.w;
+      }
+      if (a.decay_per_channel) {
+        const float4* d4 = reinterpret_cast<const float4*>(sd + t * KP);
+#pragma unroll
+        for (int i4 = 0; i4 < SCAN_KPT / 4; ++i4) {
+          const float4 dv = d4[i4 * R + r];
+          S[i4 * 4 + 0] *= dv.x; S[i4 * 4 + 1] *= dv.y; S[i4 * 4 + 2] *= dv.z; S[i4 * 4 + 3] *= dv.w;
+        }
+      } else {
+        const float d = sd[t];
+#pragma unroll
+        for (int i = 0; i < SCAN_KPT; ++i) S[i] *= d;
+      }
+      float u = sv[t * cols + cidx];
+      if (DELTA) {
+        float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < SCAN_KPT; i += 4) {
+          p0 = fmaf(S[i], kr[i], p0); p1 = fmaf(S[i + 1], kr[i + 1], p1);
+          p2 = fmaf(S[i + 2], kr[i + 2], p2); p3 = fmaf(S[i + 3], kr[i + 3], p3);
+        }
+        float p = (p0 + p1) + (p2 + p3);
+        for (int o = 1; o < R; o <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+        u = sb[t] * (u - p);
+      }
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < SCAN_KPT; i += 4) {
+        S[i] = fmaf(kr[i], u, S[i]); S[i + 1] = fmaf(kr[i + 1], u, S[i + 1]);
+        S[i + 2] = fmaf(kr[i + 2], u, S[i + 2]); S[i + 3] = fmaf(kr[i + 3], u, S[i + 3]);
+        o0 = fmaf(S[i], qr[i], o0); o1 = fmaf(S[i + 1], qr[i + 1], o1);
+        o2 = fmaf(S[i + 2], qr[i + 2], o2); o3 = fmaf(S[i + 3], qr[i + 3], o3);
+      }
+      float o = (o0 + o1) + (o2 + o3);
+      for (int w = 1; w < R; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+      if (r == 0) so[t * cols + cidx] = o + skip * sraw[t * cols + cidx];
+    }
+    __syncthreads();
+    for (int i = tid; i < nt * cols; i += SCAN_THREADS) {
+      const int t = i / cols, c = i % cols;
+      if (v0 + c < V) a.out[(size_t)(t0 + t) * a.ldo + (size_t)h * V + v0 + c] = so[i];
+    }
+  }
+
+#pragma unroll
+  for (int i = 0; i < SCAN_KPT; ++i) {
+    const int kk = ((i >> 2) * R + r) * 4 + (i & 3);
+    if (kk < K && vcol < V) st[(size_t)vcol * K + kk] = S[i];
+  }
+}
+
+static DynSmemCache g_scan_smem[4];
+
+}  // namespace b2l
+
+using namespace b2l;
+
+extern "C" int b2l_seq_scan(const b2l_seq_scan_args* a, b2l_stream_t stream) {
+  B2L_CHECK_ARG(a != nullptr, "b2l_seq_scan: null argument block");
+  B2L_CHECK_ARG(a->q && a->k && a->v && a->decay && a->state && a->meta && a->out, "b2l_seq_scan: null pointer");
+  B2L_CHECK_ARG(!a->delta || a->beta, "b2l_seq_scan: the delta rule needs beta");
+  B2L_CHECK_ARG(a->T >= 0 && a->heads > 0 && a->qk_heads > 0 && a->K > 0 && a->V > 0, "b2l_seq_scan: bad size");
+  B2L_CHECK_ARG(a->heads % a->qk_heads == 0, "b2l_seq_scan: heads %d not a multiple of qk_heads %d", a->heads, a->qk_heads);
+  B2L_CHECK_SUPPORTED(a->K <= 32 * SCAN_KPT, "b2l_seq_scan: key size %d above %d", a->K, 32 * SCAN_KPT);
+  if (a->T == 0) return 0;
+  int R = 1;
+  while (R * SCAN_KPT < a->K) R <<= 1;
+  const int KP = R * SCAN_KPT, cols = SCAN_THREADS / R;
+  const size_t smem = sizeof(float) * ((size_t)SCAN_TC * (2 * KP + (a->decay_per_channel ? KP : 1) + 3 * cols) + SCAN_TC);
+  dim3 grid((unsigned)((a->V + cols - 1) / cols), (unsigned)a->heads);
+  cudaStream_t s = (cudaStream_t)stream;
+#define B2L_SCAN_LAUNCH(D, T_, slot_)                                                     \
+  do {                                                                                    \
+    int rc_ = ensure_dyn_smem(seq_scan_kernel<D, T_>, smem, g_scan_smem[slot_]);          \
+    if (rc_) return rc_;                                                                  \
+    seq_scan_kernel<D, T_><<<grid, SCAN_THREADS, smem, s>>>(*a, R);                       \
+  } while (0)
+  if (a->act_dtype == B2L_BF16) {
+    if (a->delta) B2L_SCAN_LAUNCH(1, __nv_bfloat16, 0); else B2L_SCAN_LAUNCH(0, __nv_bfloat16, 1);
+  } else if (a->act_dtype == B2L_F32) {
+    if (a->delta) B2L_SCAN_LAUNCH(1, float, 2); else B2L_SCAN_LAUNCH(0, float, 3);
+  } else {
+    set_error("b2l_seq_scan: act_dtype %d unsupported", a->act_dtype);
+    return B2L_E_UNSUPPORTED;
+  }
+#undef B2L_SCAN_LAUNCH
+  B2L_LAUNCH_CHECK("seq_scan_kernel");
+  return 0;
+}
