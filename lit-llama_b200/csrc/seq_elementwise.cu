@@ -61,9 +61,9 @@ __global__ void __launch_bounds__(256) seq_norm_add_norm_kernel(const act_t* __r
 
 template <typename act_t>
 __global__ void seq_gated_act_kernel(const act_t* __restrict__ gu, int ldgu, act_t* __restrict__ out, int F, int act) {
-  const act_t* g = gu + (size_t)blockIdx.y * ldgu;
-  act_t* o = out + (size_t)blockIdx.y * F;
-  for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < F; j += gridDim.x * blockDim.x) {
+  const act_t* g = gu + (size_t)blockIdx.x * ldgu;
+  act_t* o = out + (size_t)blockIdx.x * F;
+  for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < F; j += gridDim.y * blockDim.x) {
     const float a = ld_act(g, j), b = ld_act(g, (size_t)F + j);
     const float f = act == B2L_SEQ_ACT_GELU_TANH ? gelu_tanh_f(a) : (act == B2L_SEQ_ACT_SILU ? silu_f(a) : sigmoid_f(a));
     st_act(o, j, f * b);
@@ -151,19 +151,19 @@ __global__ void seq_decay_kernel(const act_t* __restrict__ a, int lda, const act
                                  const act_t* __restrict__ A_log, int mode, float inv_tau, float* __restrict__ out,
                                  float* __restrict__ dt_out, int heads, int size) {
   const int n = heads * size;
-  const act_t* ar = a + (size_t)blockIdx.y * lda;
-  for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < n; j += gridDim.x * blockDim.x) {
+  const act_t* ar = a + (size_t)blockIdx.x * lda;
+  for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < n; j += gridDim.y * blockDim.x) {
     const float z = ld_act(ar, j) + (bias ? ld_act(bias, j) : 0.f);
     float r;
     if (mode == B2L_SEQ_DECAY_EXP_SOFTPLUS) {
       const float dt = softplus_f(z);
-      if (dt_out) dt_out[(size_t)blockIdx.y * n + j] = dt;
+      if (dt_out) dt_out[(size_t)blockIdx.x * n + j] = dt;
       r = expf(-expf(ld_act(A_log, j / size)) * dt);
     } else {
       // sigmoid(z)^(1/tau) = exp(-softplus(-z) / tau): no underflow of the sigmoid for very negative z
       r = expf(-softplus_f(-z) * inv_tau);
     }
-    out[(size_t)blockIdx.y * n + j] = r;
+    out[(size_t)blockIdx.x * n + j] = r;
   }
 }
 
@@ -280,7 +280,7 @@ extern "C" int b2l_seq_gated_act(const void* gu, int ldgu, void* out, int T, int
   B2L_CHECK_ARG(T >= 0 && F > 0 && ldgu >= 2 * F, "b2l_seq_gated_act: bad size");
   B2L_CHECK_ARG(act >= 0 && act <= 2, "b2l_seq_gated_act: unknown activation %d", act);
   if (T == 0) return 0;
-  dim3 grid((unsigned)std::min((F + 255) / 256, 64), (unsigned)T);
+  dim3 grid((unsigned)T, (unsigned)std::min((F + 255) / 256, 64));
   B2L_SEQ_DISPATCH(act_dtype, (seq_gated_act_kernel<act_t><<<grid, 256, 0, (cudaStream_t)stream>>>((const act_t*)gu, ldgu, (act_t*)out, F, act)));
   B2L_LAUNCH_CHECK("seq_gated_act_kernel");
   return 0;
@@ -322,7 +322,7 @@ extern "C" int b2l_seq_decay(const void* a, int lda, const void* bias, const voi
   B2L_CHECK_ARG(mode != B2L_SEQ_DECAY_SIGMOID_ROOT || tau > 0.f, "b2l_seq_decay: tau must be positive");
   if (T == 0) return 0;
   const int n = heads * size;
-  dim3 grid((unsigned)std::min((n + 255) / 256, 64), (unsigned)T);
+  dim3 grid((unsigned)T, (unsigned)std::min((n + 255) / 256, 64));
   B2L_SEQ_DISPATCH(act_dtype, (seq_decay_kernel<act_t><<<grid, 256, 0, (cudaStream_t)stream>>>(
                                   (const act_t*)a, lda, (const act_t*)bias, (const act_t*)A_log, mode, mode == B2L_SEQ_DECAY_SIGMOID_ROOT ? 1.0f / tau : 0.f,
                                   out, dt_out, heads, size)));

@@ -30,7 +30,11 @@ class StepContext:
     def __init__(self, T: int, meta: torch.Tensor, state: Dict[str, torch.Tensor], dtype: torch.dtype) -> None:
         self.T, self.meta, self.state, self.dtype = T, meta, state, dtype
         self.act = S.act_code(dtype)
-        self.stream = S.stream_ptr()
+
+    @property
+    def stream(self) -> int:
+        """The current CUDA stream at the time of each launch (the capturing stream while a graph is recorded)."""
+        return S.stream_ptr()
 
 
 def _p(t: Optional[torch.Tensor], offset: int = 0) -> Optional[int]:

@@ -58,11 +58,10 @@ class SequenceStatePool:
         if not self._free:
             raise PoolFull(f"all {self.n_slots} state slots are in use")
         slot = self._free.pop()
-        lib, stream = S.lib(), S.stream_ptr()
         for name, sp in self.specs.items():
             if sp.zero_on_acquire:
                 t = self.tensors[name]
-                S.check(lib.b2l_seq_zero_slot(t.data_ptr(), t[0].numel() * t.element_size(), slot, stream), "b2l_seq_zero_slot")
+                S.check(S.lib().b2l_seq_zero_slot(t.data_ptr(), t[0].numel() * t.element_size(), slot, S.stream_ptr()), "b2l_seq_zero_slot")
         self._slot_of[request_id] = slot
         self._pos[slot] = 0
         self.acquired += 1

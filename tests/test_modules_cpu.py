@@ -104,7 +104,7 @@ def test_product_does_not_import_the_oracle():
                 assert "oracle" not in src, f"{f} references oracle/"
 
 
-@pytest.mark.skipif(not os.path.isdir(REF), reason="reference checkout not present")
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lit_llama")), reason="reference checkout not present")
 def test_patch_reference_plugs_into_unmodified_reference():
     here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     sys.path.insert(0, os.path.join(here, "oracle", "_shim"))
