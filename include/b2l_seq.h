@@ -73,10 +73,10 @@ int b2l_seq_decay(const void* a, int lda, const void* bias, const void* A_log, i
  * with v'_t = v_t * vscale[t, head] when vscale is given.  q and k have `qk_heads` heads, value head h reads
  * q/k head h / (heads / qk_heads).  `state` is [n_slots][heads][V][K] f32 (key channel fastest). */
 typedef struct {
-  const void* q; int ldq;                   /* f32, or act when qkv_act != 0 */
-  const void* k; int ldk;
-  const void* v; int ldv;
-  int qkv_act; float q_mult;                /* q is multiplied by q_mult when it is read */
+  const float* q; int ldq;
+  const float* k; int ldk;
+  const float* v; int ldv;
+  float q_mult;                             /* o_t = q_mult * S^T q_t */
   const float* decay; int ldd; int decay_per_channel;
   const void* beta; int ldb; int delta;     /* act [T, ldb], one per head; read only when delta != 0 */
   const float* vscale; int ldvs;            /* f32 [T, heads] or null */
@@ -119,6 +119,9 @@ typedef struct {
   int has_sink, block, T, heads, kv_heads, K, V, act_dtype;
 } b2l_seq_attn_args;
 int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t stream);
+
+/* out[t, j] = (float) in[t, j]: act columns of a product as f32 operands of a recurrence. */
+int b2l_seq_cast_f32(const void* in, int ldin, float* out, int ldout, int T, int n, int act_dtype, b2l_stream_t stream);
 
 /* Zero one slot of a state tensor laid out [n_slots][slot_bytes]. */
 int b2l_seq_zero_slot(void* state, size_t slot_bytes, int slot, b2l_stream_t stream);

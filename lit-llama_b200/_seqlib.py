@@ -19,7 +19,7 @@ class ScanArgs(C.Structure):
         ("q", c_void_p), ("ldq", c_int),
         ("k", c_void_p), ("ldk", c_int),
         ("v", c_void_p), ("ldv", c_int),
-        ("qkv_act", c_int), ("q_mult", c_float),
+        ("q_mult", c_float),
         ("decay", c_void_p), ("ldd", c_int), ("decay_per_channel", c_int),
         ("beta", c_void_p), ("ldb", c_int), ("delta", c_int),
         ("vscale", c_void_p), ("ldvs", c_int),
@@ -63,6 +63,7 @@ _SIGS = {
     "b2l_seq_headnorm_rope": (c_int, [c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_int,
                                       c_int, c_int, c_int, c_void_p]),
     "b2l_seq_block_attention": (c_int, [C.POINTER(AttnArgs), c_void_p]),
+    "b2l_seq_cast_f32": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "b2l_seq_zero_slot": (c_int, [c_void_p, c_size_t, c_int, c_void_p]),
 }
 

@@ -146,6 +146,186 @@ __global__ void __launch_bounds__(128) seq_block_attention_kernel(b2l_seq_attn_a
   }
 }
 
+// ---- prompt portions: a CTA computes TQ queries of one head against key tiles of TK positions, SGEMM style.
+// Scores: thread (ty, tx) holds queries ty + 16 i and keys tx + 8 j (4 x 4) with q and k rows read as float4 from
+// padded shared memory; the 8 lanes of a ty group share their rows' maxima and sums by shuffles; the weights go
+// through shared memory into the value product, where the same thread holds its 4 queries x V/8 value channels.
+// All in f32 on the CUDA cores: the design wants scores and weights in 32-bit, which the tensor cores do not give.
+constexpr int TQ = 64, TK = 32, TILE_THREADS = 128;
+
+template <typename act_t>
+__device__ __forceinline__ float4 ld4_act(const act_t* p);
+template <>
+__device__ __forceinline__ float4 ld4_act<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <>
+__device__ __forceinline__ float4 ld4_act<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 w = *reinterpret_cast<const uint2*>(p);
+  return make_float4(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xffff0000u), __uint_as_float(w.y << 16), __uint_as_float(w.y & 0xffff0000u));
+}
+
+template <typename act_t, int VC>
+__global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(b2l_seq_attn_args a) {
+  extern __shared__ __align__(16) float smem[];
+  const int K = a.K, V = 32 * VC, Kp = K + 4;
+  float* sQ = smem;                    // [TQ][Kp]
+  float* sK = sQ + TQ * Kp;            // [TK][Kp]
+  float* sV = sK + TK * Kp;            // [TK][V]
+  float* sP = sV + TK * V;             // [TQ][TK + 1]
+  const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;
+  const int h = blockIdx.y, g = h / (a.heads / a.kv_heads);
+  const int t_first = blockIdx.x * TQ, nq = min(TQ, a.T - t_first);
+  const int slot = a.meta[0], pos0 = a.meta[1];
+  const int p_first = pos0 + t_first, p_last = p_first + nq - 1;
+  const int j_begin = (p_first / a.block) * a.block;
+
+  const act_t* kn = (const act_t*)a.k_new;
+  const act_t* vn = (const act_t*)a.v_new;
+  const act_t* ck = (const act_t*)a.cache_k + (size_t)slot * a.block * a.kv_heads * K;
+  const act_t* cv = (const act_t*)a.cache_v + (size_t)slot * a.block * a.kv_heads * V;
+
+  const int K4 = K >> 2;
+  for (int i = tid; i < TQ * K4; i += TILE_THREADS) {
+    const int r = i / K4, c = (i - r * K4) << 2;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < nq) v = *reinterpret_cast<const float4*>(a.q + ((size_t)(t_first + r) * a.heads + h) * K + c);
+    *reinterpret_cast<float4*>(sQ + r * Kp + c) = v;
+  }
+
+  float m[4], l[4], acc[4][VC][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    m[i] = a.has_sink ? 0.f : -INFINITY;
+    l[i] = a.has_sink ? 1.f : 0.f;
+#pragma unroll
+    for (int c = 0; c < VC; ++c) acc[i][c][0] = acc[i][c][1] = acc[i][c][2] = acc[i][c][3] = 0.f;
+  }
+
+  for (int jb = j_begin; jb <= p_last; jb += TK) {
+    __syncthreads();                   // the previous tile's K, V and P are no longer read (and sQ is written)
+    for (int i = tid; i < TK * K4; i += TILE_THREADS) {
+      const int r = i / K4, c = (i - r * K4) << 2, j = jb + r;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j <= p_last) {
+        const int e = j % a.block;
+        v = ld4_act<act_t>(j >= pos0 ? kn + ((size_t)(j - pos0) * a.kv_heads + g) * K + c : ck + ((size_t)e * a.kv_heads + g) * K + c);
+      }
+      *reinterpret_cast<float4*>(sK + r * Kp + c) = v;
+    }
+    for (int i = tid; i < TK * (V >> 2); i += TILE_THREADS) {
+      const int r = i / (V >> 2), c = (i - r * (V >> 2)) << 2, j = jb + r;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j <= p_last) {
+        const int e = j % a.block;
+        v = ld4_act<act_t>(j >= pos0 ? vn + (size_t)(j - pos0) * a.ldv + (size_t)g * V + c : cv + ((size_t)e * a.kv_heads + g) * V + c);
+      }
+      *reinterpret_cast<float4*>(sV + r * V + c) = v;
+    }
+    __syncthreads();
+
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+    for (int c = 0; c < K; c += 4) {
+      float4 qv[4], kv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4*>(sQ + (ty + 16 * i) * Kp + c);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) kv[j] = *reinterpret_cast<const float4*>(sK + (tx + 8 * j) * Kp + c);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          s[i][j] = fmaf(qv[i].x, kv[j].x, s[i][j]);
+          s[i][j] = fmaf(qv[i].y, kv[j].y, s[i][j]);
+          s[i][j] = fmaf(qv[i].z, kv[j].z, s[i][j]);
+          s[i][j] = fmaf(qv[i].w, kv[j].w, s[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int p = p_first + ty + 16 * i;          // this row's position (rows beyond nq are never stored)
+      const int c0 = (p / a.block) * a.block;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int key = jb + tx + 8 * j;
+        float v = s[i][j] * a.scale;
+        if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
+        v = (key <= p && key >= c0) ? v : -INFINITY;
+        s[i][j] = v;
+        mx = fmaxf(mx, v);
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      const float mn = fmaxf(m[i], mx);
+      const float corr = (mn == -INFINITY) ? 1.f : expf(m[i] - mn);
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float w = (s[i][j] == -INFINITY) ? 0.f : expf(s[i][j] - mn);
+        sP[(ty + 16 * i) * (TK + 1) + tx + 8 * j] = w;
+        sum += w;
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      l[i] = l[i] * corr + sum;
+      m[i] = mn;
+#pragma unroll
+      for (int c = 0; c < VC; ++c) {
+        acc[i][c][0] *= corr; acc[i][c][1] *= corr; acc[i][c][2] *= corr; acc[i][c][3] *= corr;
+      }
+    }
+    __syncwarp();                      // a row's weights are written and read by the 8 lanes of one ty group
+    const int nk = min(TK, p_last - jb + 1);
+    for (int j = 0; j < nk; ++j) {
+      float w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) w[i] = sP[(ty + 16 * i) * (TK + 1) + j];
+#pragma unroll
+      for (int c = 0; c < VC; ++c) {
+        const float4 v = *reinterpret_cast<const float4*>(sV + j * V + tx * 4 + 32 * c);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[i][c][0] = fmaf(w[i], v.x, acc[i][c][0]); acc[i][c][1] = fmaf(w[i], v.y, acc[i][c][1]);
+          acc[i][c][2] = fmaf(w[i], v.z, acc[i][c][2]); acc[i][c][3] = fmaf(w[i], v.w, acc[i][c][3]);
+        }
+      }
+    }
+  }
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = ty + 16 * i;
+    if (r >= nq) continue;
+    const int t = t_first + r;
+    float f = a.out_mult / l[i];
+    if (a.gate) f *= sigmoid_f(ld_act((const act_t*)a.gate, (size_t)t * a.ldg + h));
+    act_t* o = (act_t*)a.out + (size_t)t * a.ldo + (size_t)h * V;
+#pragma unroll
+    for (int c = 0; c < VC; ++c) {
+      const int ch = tx * 4 + 32 * c;
+      st_act(o, ch + 0, acc[i][c][0] * f); st_act(o, ch + 1, acc[i][c][1] * f);
+      st_act(o, ch + 2, acc[i][c][2] * f); st_act(o, ch + 3, acc[i][c][3] * f);
+    }
+  }
+}
+
+static DynSmemCache g_tile_smem[8];
+
+template <typename act_t, int VC>
+static int launch_tile(const b2l_seq_attn_args* a, cudaStream_t s, int cache_slot) {
+  const size_t smem = sizeof(float) * ((size_t)(TQ + TK) * (a->K + 4) + (size_t)TK * 32 * VC + (size_t)TQ * (TK + 1));
+  int rc = ensure_dyn_smem(seq_block_attention_tile_kernel<act_t, VC>, smem, g_tile_smem[cache_slot]);
+  if (rc) return rc;
+  dim3 grid((unsigned)((a->T + TQ - 1) / TQ), (unsigned)a->heads);
+  seq_block_attention_tile_kernel<act_t, VC><<<grid, TILE_THREADS, smem, s>>>(*a);
+  return 0;
+}
+
 // ring[p % block] <- token p for the portion's tokens in the block of its last token.
 template <typename act_t>
 __global__ void seq_ring_append_kernel(b2l_seq_attn_args a) {
@@ -184,7 +364,20 @@ extern "C" int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t 
   const bool split = pairs < 2 * sm_count();          // few queries (decoding): four warps share one query's keys
   const size_t smem = sizeof(float) * ((size_t)(split ? 1 : 4) * Kpad + 4 * (2 + ATT_VMAX * 32));
   B2L_CHECK_SUPPORTED(smem <= 48 * 1024, "b2l_seq_block_attention: key size %d too large", a->K);
-  if (a->act_dtype == B2L_BF16) {
+  const bool al = (((uintptr_t)a->q | (uintptr_t)a->k_new | (uintptr_t)a->v_new | (uintptr_t)a->cache_k | (uintptr_t)a->cache_v) % 16) == 0;
+  const size_t tile_smem = sizeof(float) * ((size_t)(TQ + TK) * (a->K + 4) + (size_t)TK * a->V + (size_t)TQ * (TK + 1));
+  const bool tile = !split && a->T >= 16 && al && a->K % 4 == 0 && a->V % 32 == 0 && a->V <= 128 && a->ldv % 4 == 0 && tile_smem <= 200 * 1024;
+  if (tile) {
+    const int vc = a->V / 32;
+    int rc = 0;
+    if (a->act_dtype == B2L_BF16)
+      rc = vc == 1 ? launch_tile<__nv_bfloat16, 1>(a, s, 0) : vc == 2 ? launch_tile<__nv_bfloat16, 2>(a, s, 1)
+         : vc == 3 ? launch_tile<__nv_bfloat16, 3>(a, s, 2) : launch_tile<__nv_bfloat16, 4>(a, s, 3);
+    else
+      rc = vc == 1 ? launch_tile<float, 1>(a, s, 4) : vc == 2 ? launch_tile<float, 2>(a, s, 5)
+         : vc == 3 ? launch_tile<float, 3>(a, s, 6) : launch_tile<float, 4>(a, s, 7);
+    if (rc) return rc;
+  } else if (a->act_dtype == B2L_BF16) {
     if (split) seq_block_attention_kernel<__nv_bfloat16, 4><<<pairs, 128, smem, s>>>(*a, vec);
     else seq_block_attention_kernel<__nv_bfloat16, 1><<<(pairs + 3) / 4, 128, smem, s>>>(*a, vec);
   } else {

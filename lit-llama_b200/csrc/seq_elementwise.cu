@@ -134,6 +134,13 @@ __global__ void seq_conv_state_kernel(const act_t* __restrict__ in, int ldin, ac
   for (int j = 0; j < taps - 1; ++j) st[(size_t)j * C + c] = in[(size_t)(T - (taps - 1) + j) * ldin + c];
 }
 
+template <typename act_t>
+__global__ void seq_cast_f32_kernel(const act_t* __restrict__ in, int ldin, float* __restrict__ out, int ldout, int n) {
+  const act_t* p = in + (size_t)blockIdx.x * ldin;
+  float* q = out + (size_t)blockIdx.x * ldout;
+  for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < n; j += gridDim.y * blockDim.x) q[j] = ld_act(p, j);
+}
+
 // One warp per (token, head): x * mult / sqrt(sum x^2 + eps), in place.
 __global__ void seq_unit_norm_kernel(float* __restrict__ x, int ld, int n_groups, int heads, int size, float eps, float mult) {
   const int g = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -301,6 +308,16 @@ extern "C" int b2l_seq_conv_silu(const void* in, int ldin, const void* w, const 
       seq_conv_state_kernel<act_t><<<(C + 127) / 128, 128, 0, (cudaStream_t)stream>>>((const act_t*)in, ldin, (act_t*)state, meta, T, C, taps);
   });
   B2L_LAUNCH_CHECK("seq_conv_silu_kernel");
+  return 0;
+}
+
+extern "C" int b2l_seq_cast_f32(const void* in, int ldin, float* out, int ldout, int T, int n, int act_dtype, b2l_stream_t stream) {
+  B2L_CHECK_ARG(in && out, "b2l_seq_cast_f32: null pointer");
+  B2L_CHECK_ARG(T >= 0 && n > 0 && ldin >= n && ldout >= n, "b2l_seq_cast_f32: bad size");
+  if (T == 0) return 0;
+  dim3 grid((unsigned)T, (unsigned)std::min((n + 255) / 256, 64));
+  B2L_SEQ_DISPATCH(act_dtype, (seq_cast_f32_kernel<act_t><<<grid, 256, 0, (cudaStream_t)stream>>>((const act_t*)in, ldin, out, ldout, n)));
+  B2L_LAUNCH_CHECK("seq_cast_f32_kernel");
   return 0;
 }
 

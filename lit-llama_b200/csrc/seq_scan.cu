@@ -5,7 +5,7 @@
 // lanes (SCAN_KPT numbers each), so a step is R-lane shuffles and no shared-memory traffic for S.  The state is
 // read once, carried through all T tokens of the portion and written once ([V][K] per head, K fastest, so the R
 // lanes of a column read consecutive 16-byte words).  Inputs of SCAN_TC steps are staged in shared memory by the
-// whole CTA.  All arithmetic is f32.
+// whole CTA with asynchronous copies, one stage ahead of the recurrence.  All arithmetic is f32.
 #include "seq_common.cuh"
 
 namespace b2l {
@@ -14,24 +14,27 @@ constexpr int SCAN_KPT = 16;       // state numbers per lane
 constexpr int SCAN_TC = 16;        // steps per shared-memory stage
 constexpr int SCAN_THREADS = 128;
 
-template <typename act_t>
-__device__ __forceinline__ float ld_in(const void* p, int is_act, size_t i) {
-  return is_act ? ld_act((const act_t*)p, i) : ((const float*)p)[i];
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// Inputs of SCAN_TC steps go to shared memory with cp.async, two stages deep: stage s+1 is in flight while the
+// recurrence runs over stage s, so the sequential loop never waits on global memory after the first stage.
+// Stage layout: q[TC][KP] k[TC][KP] d[TC][DP] v[TC][cols] vs[TC] beta[TC] (+ 2*TC unused: stages stay 16-byte aligned).
 template <int DELTA, typename act_t>
-__global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_args a, int R) {
-  extern __shared__ float smem[];
+__global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_args a, int R, int vec) {
+  extern __shared__ __align__(16) float smem[];
   const int KP = R * SCAN_KPT;                 // padded key size
   const int cols = SCAN_THREADS / R;           // value columns of this CTA
-  const int DP = a.decay_per_channel ? KP : 1;
-  float* sq = smem;                            // [TC][KP]
-  float* sk = sq + SCAN_TC * KP;               // [TC][KP]
-  float* sd = sk + SCAN_TC * KP;               // [TC][DP]
-  float* sv = sd + SCAN_TC * DP;               // [TC][cols]  v' (scaled)
-  float* sraw = sv + SCAN_TC * cols;           // [TC][cols]  v as given (skip term)
-  float* so = sraw + SCAN_TC * cols;           // [TC][cols]
-  float* sb = so + SCAN_TC * cols;             // [TC] sigmoid(beta)
+  const int DP = a.decay_per_channel ? KP : 4;
+  const int stage = SCAN_TC * (2 * KP + DP + cols + 4);
+  const int beta_at = SCAN_TC * (2 * KP + DP + cols + 1);
+  float* so = smem + 2 * stage;                // [TC][cols]
 
   const int tid = threadIdx.x, r = tid % R, cidx = tid / R;
   const int h = blockIdx.y, hq = h / (a.heads / a.qk_heads);
@@ -40,6 +43,67 @@ __global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_arg
   const int slot = a.meta[0];
   float* st = a.state + ((size_t)slot * a.heads + h) * (size_t)V * K;
   const float skip = a.skip ? ld_act((const act_t*)a.skip, h) : 0.f;
+  const float* gq = a.q + (size_t)hq * K;
+  const float* gk = a.k + (size_t)hq * K;
+  const float* gv = a.v + (size_t)h * V + v0;
+  const float* gd = a.decay + (a.decay_per_channel ? (size_t)h * K : (size_t)h);
+  const int ncol = min(cols, V - v0);
+
+  // padding that no copy ever touches: q = k = 0 and d = 1 beyond K, v = 0 beyond V, vs = 1 without a value scale
+  for (int b = 0; b < 2; ++b) {
+    float* sq = smem + b * stage;
+    float* sk = sq + SCAN_TC * KP;
+    float* sd = sk + SCAN_TC * KP;
+    float* sv = sd + SCAN_TC * DP;
+    float* svs = sv + SCAN_TC * cols;
+    for (int i = tid; i < SCAN_TC * KP; i += SCAN_THREADS) {
+      if (i % KP >= K) {
+        sq[i] = 0.f;
+        sk[i] = 0.f;
+        if (a.decay_per_channel) sd[i] = 1.f;
+      }
+    }
+    for (int i = tid; i < SCAN_TC * cols; i += SCAN_THREADS)
+      if (i % cols >= ncol) sv[i] = 0.f;
+    if (tid < SCAN_TC) svs[tid] = 1.f;
+  }
+
+  auto prefetch = [&](int t0, int b) {
+    const int nt = min(SCAN_TC, a.T - t0);
+    float* sq = smem + b * stage;
+    float* sk = sq + SCAN_TC * KP;
+    float* sd = sk + SCAN_TC * KP;
+    float* sv = sd + SCAN_TC * DP;
+    float* svs = sv + SCAN_TC * cols;
+    if (vec) {
+      const int K4 = K >> 2;
+      for (int i = tid; i < nt * K4; i += SCAN_THREADS) {
+        const int t = i / K4, kk = (i - t * K4) << 2;
+        cp_async16(sq + t * KP + kk, gq + (size_t)(t0 + t) * a.ldq + kk);
+        cp_async16(sk + t * KP + kk, gk + (size_t)(t0 + t) * a.ldk + kk);
+        if (a.decay_per_channel) cp_async16(sd + t * KP + kk, gd + (size_t)(t0 + t) * a.ldd + kk);
+      }
+    } else {
+      for (int i = tid; i < nt * K; i += SCAN_THREADS) {
+        const int t = i / K, kk = i - t * K;
+        cp_async4(sq + t * KP + kk, gq + (size_t)(t0 + t) * a.ldq + kk);
+        cp_async4(sk + t * KP + kk, gk + (size_t)(t0 + t) * a.ldk + kk);
+        if (a.decay_per_channel) cp_async4(sd + t * KP + kk, gd + (size_t)(t0 + t) * a.ldd + kk);
+      }
+    }
+    for (int i = tid; i < nt * ncol; i += SCAN_THREADS) {
+      const int t = i / ncol, c = i - t * ncol;
+      cp_async4(sv + t * cols + c, gv + (size_t)(t0 + t) * a.ldv + c);
+    }
+    if (tid < nt) {
+      if (!a.decay_per_channel) cp_async4(sd + tid, gd + (size_t)(t0 + tid) * a.ldd);
+      if (a.vscale) cp_async4(svs + tid, a.vscale + (size_t)(t0 + tid) * a.ldvs + h);
+    }
+    cp_async_commit();
+  };
+  auto beta_of = [&](int t0) -> float {   // raw gate of step t0 + tid: act-typed, so a plain load kept in a register
+    return (DELTA && tid < min(SCAN_TC, a.T - t0)) ? ld_act((const act_t*)a.beta, (size_t)(t0 + tid) * a.ldb + h) : 0.f;
+  };
 
   float S[SCAN_KPT];
 #pragma unroll
@@ -48,28 +112,29 @@ __global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_arg
     S[i] = (kk < K && vcol < V) ? st[(size_t)vcol * K + kk] : 0.f;
   }
 
-  for (int t0 = 0; t0 < a.T; t0 += SCAN_TC) {
+  __syncthreads();                    // the padding is written before any copy lands next to it
+  prefetch(0, 0);
+  if (DELTA && tid < SCAN_TC) smem[beta_at + tid] = sigmoid_f(beta_of(0));
+
+  int b = 0;
+  for (int t0 = 0; t0 < a.T; t0 += SCAN_TC, b ^= 1) {
     const int nt = min(SCAN_TC, a.T - t0);
-    __syncthreads();   // the previous stage's so[] has been written out
-    for (int i = tid; i < nt * KP; i += SCAN_THREADS) {
-      const int t = i / KP, kk = i % KP;
-      const bool in = kk < K;
-      sq[i] = in ? ld_in<act_t>(a.q, a.qkv_act, (size_t)(t0 + t) * a.ldq + (size_t)hq * K + kk) * a.q_mult : 0.f;
-      sk[i] = in ? ld_in<act_t>(a.k, a.qkv_act, (size_t)(t0 + t) * a.ldk + (size_t)hq * K + kk) : 0.f;
-      if (a.decay_per_channel) sd[i] = in ? a.decay[(size_t)(t0 + t) * a.ldd + (size_t)h * K + kk] : 1.f;
+    const bool more = t0 + SCAN_TC < a.T;
+    float beta_next = 0.f;
+    if (more) {
+      prefetch(t0 + SCAN_TC, b ^ 1);
+      beta_next = beta_of(t0 + SCAN_TC);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
-    for (int i = tid; i < nt * cols; i += SCAN_THREADS) {
-      const int t = i / cols, c = i % cols;
-      float v = 0.f;
-      if (v0 + c < V) v = ld_in<act_t>(a.v, a.qkv_act, (size_t)(t0 + t) * a.ldv + (size_t)h * V + v0 + c);
-      sraw[i] = v;
-      sv[i] = a.vscale ? v * a.vscale[(size_t)(t0 + t) * a.ldvs + h] : v;
-    }
-    if (tid < nt) {
-      if (!a.decay_per_channel) sd[tid] = a.decay[(size_t)(t0 + tid) * a.ldd + h];
-      if (DELTA) sb[tid] = sigmoid_f(ld_act((const act_t*)a.beta, (size_t)(t0 + tid) * a.ldb + h));
-    }
-    __syncthreads();
+    __syncthreads();                  // stage t0 has landed for every thread; so[] of the previous stage is written out
+    const float* sq = smem + b * stage;
+    const float* sk = sq + SCAN_TC * KP;
+    const float* sd = sk + SCAN_TC * KP;
+    const float* sv = sd + SCAN_TC * DP;
+    const float* svs = sv + SCAN_TC * cols;
+    const float* sb = svs + SCAN_TC;
 
     for (int t = 0; t < nt; ++t) {
       const float4* q4 = reinterpret_cast<const float4*>(sq + t * KP);
@@ -93,7 +158,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_arg
 #pragma unroll
         for (int i = 0; i < SCAN_KPT; ++i) S[i] *= d;
       }
-      float u = sv[t * cols + cidx];
+      const float vraw = sv[t * cols + cidx];
+      float u = vraw * svs[t];
       if (DELTA) {
         float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
 #pragma unroll
@@ -115,13 +181,14 @@ __global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_arg
       }
       float o = (o0 + o1) + (o2 + o3);
       for (int w = 1; w < R; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
-      if (r == 0) so[t * cols + cidx] = o + skip * sraw[t * cols + cidx];
+      if (r == 0) so[t * cols + cidx] = o * a.q_mult + skip * vraw;
     }
     __syncthreads();
-    for (int i = tid; i < nt * cols; i += SCAN_THREADS) {
-      const int t = i / cols, c = i % cols;
-      if (v0 + c < V) a.out[(size_t)(t0 + t) * a.ldo + (size_t)h * V + v0 + c] = so[i];
+    for (int i = tid; i < nt * ncol; i += SCAN_THREADS) {
+      const int t = i / ncol, c = i - t * ncol;
+      a.out[(size_t)(t0 + t) * a.ldo + (size_t)h * V + v0 + c] = so[t * cols + c];
     }
+    if (DELTA && more && tid < SCAN_TC) smem[(b ^ 1) * stage + beta_at + tid] = sigmoid_f(beta_next);
   }
 
 #pragma unroll
@@ -148,14 +215,17 @@ extern "C" int b2l_seq_scan(const b2l_seq_scan_args* a, b2l_stream_t stream) {
   int R = 1;
   while (R * SCAN_KPT < a->K) R <<= 1;
   const int KP = R * SCAN_KPT, cols = SCAN_THREADS / R;
-  const size_t smem = sizeof(float) * ((size_t)SCAN_TC * (2 * KP + (a->decay_per_channel ? KP : 1) + 3 * cols) + SCAN_TC);
+  const size_t smem = sizeof(float) * (2 * (size_t)SCAN_TC * (2 * KP + (a->decay_per_channel ? KP : 4) + cols + 4) + (size_t)SCAN_TC * cols);
+  auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  const int vec = a->K % 4 == 0 && a->ldq % 4 == 0 && a->ldk % 4 == 0 && al16(a->q) && al16(a->k) &&
+                  (!a->decay_per_channel || (a->ldd % 4 == 0 && al16(a->decay)));
   dim3 grid((unsigned)((a->V + cols - 1) / cols), (unsigned)a->heads);
   cudaStream_t s = (cudaStream_t)stream;
 #define B2L_SCAN_LAUNCH(D, T_, slot_)                                                     \
   do {                                                                                    \
     int rc_ = ensure_dyn_smem(seq_scan_kernel<D, T_>, smem, g_scan_smem[slot_]);          \
     if (rc_) return rc_;                                                                  \
-    seq_scan_kernel<D, T_><<<grid, SCAN_THREADS, smem, s>>>(*a, R);                       \
+    seq_scan_kernel<D, T_><<<grid, SCAN_THREADS, smem, s>>>(*a, R, vec);                      \
   } while (0)
   if (a->act_dtype == B2L_BF16) {
     if (a->delta) B2L_SCAN_LAUNCH(1, __nv_bfloat16, 0); else B2L_SCAN_LAUNCH(0, __nv_bfloat16, 1);

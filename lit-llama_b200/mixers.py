@@ -88,9 +88,9 @@ class GatedMLP:
 
 
 # ------------------------------------------------------------------------------------------------ recurrences
-def _scan(ctx: StepContext, *, q, ldq, k, ldk, v, ldv, qkv_act, q_mult, decay, ldd, per_channel, state, out, ldo, heads, qk_heads,
+def _scan(ctx: StepContext, *, q, ldq, k, ldk, v, ldv, q_mult, decay, ldd, per_channel, state, out, ldo, heads, qk_heads,
           K, V, beta=None, ldb=0, vscale=None, ldvs=0, skip=None) -> None:
-    a = S.ScanArgs(q=q, ldq=ldq, k=k, ldk=ldk, v=v, ldv=ldv, qkv_act=int(qkv_act), q_mult=float(q_mult), decay=decay, ldd=ldd,
+    a = S.ScanArgs(q=q, ldq=ldq, k=k, ldk=ldk, v=v, ldv=ldv, q_mult=float(q_mult), decay=decay, ldd=ldd,
                    decay_per_channel=int(per_channel), beta=beta, ldb=ldb, delta=int(beta is not None), vscale=vscale, ldvs=ldvs,
                    skip=skip, state=_p(state), meta=_p(ctx.meta), out=out, ldo=ldo, T=ctx.T, heads=heads, qk_heads=qk_heads, K=K, V=V,
                    act_dtype=ctx.act)
@@ -138,7 +138,7 @@ class ChannelDeltaMixer:
         S.check(lib.b2l_seq_decay(_p(a), self.H * self.K, _p(self.dt_bias), _p(self.A_log), S.DECAY_EXP_SOFTPLUS, 0.0, _p(g), None, T,
                                   self.H, self.K, ctx.act, ctx.stream), "b2l_seq_decay")
         o = torch.empty((T, self.H * self.V), dtype=torch.float32, device=dev)
-        _scan(ctx, q=_p(qkv, self.o_q), ldq=self.C, k=_p(qkv, self.o_k), ldk=self.C, v=_p(qkv, self.o_v), ldv=self.C, qkv_act=False,
+        _scan(ctx, q=_p(qkv, self.o_q), ldq=self.C, k=_p(qkv, self.o_k), ldk=self.C, v=_p(qkv, self.o_v), ldv=self.C,
               q_mult=1.0, decay=_p(g), ldd=self.H * self.K, per_channel=True, beta=_p(proj, self.o_b), ldb=self.n_in,
               state=ctx.state[self.name + ".S"], out=_p(o), ldo=self.H * self.V, heads=self.H, qk_heads=self.G, K=self.K, V=self.V)
         y = torch.empty((T, self.H * self.V), dtype=h.dtype, device=dev)
@@ -180,7 +180,7 @@ class Mamba2Mixer:
                                   _p(dt), T, self.H, 1, ctx.act, ctx.stream), "b2l_seq_decay")
         y = torch.empty((T, self.inner), dtype=torch.float32, device=dev)
         GN = self.G * self.N
-        _scan(ctx, q=_p(xbc, self.inner + GN), ldq=self.C, k=_p(xbc, self.inner), ldk=self.C, v=_p(xbc), ldv=self.C, qkv_act=False, q_mult=1.0,
+        _scan(ctx, q=_p(xbc, self.inner + GN), ldq=self.C, k=_p(xbc, self.inner), ldk=self.C, v=_p(xbc), ldv=self.C, q_mult=1.0,
               decay=_p(decay), ldd=self.H, per_channel=False, vscale=_p(dt), ldvs=self.H, skip=_p(self.D), state=ctx.state[self.name + ".S"],
               out=_p(y), ldo=self.inner, heads=self.H, qk_heads=self.G, K=self.N, V=self.P)
         out = torch.empty((T, self.inner), dtype=h.dtype, device=dev)
@@ -293,7 +293,10 @@ class GatedLinearAttention:
         S.check(lib.b2l_seq_decay(_p(a), n, _p(self.b_a2), None, S.DECAY_SIGMOID_ROOT, self.tau, _p(alpha), None, T, self.H, self.K, ctx.act,
                                   ctx.stream), "b2l_seq_decay")
         o = torch.empty((T, self.H * self.V), dtype=torch.float32, device=dev)
-        _scan(ctx, q=_p(proj, o_q), ldq=ld, k=_p(proj, o_k), ldk=ld, v=_p(proj, o_v), ldv=ld, qkv_act=True, q_mult=self.K ** -0.5, decay=_p(alpha),
+        nq = o_g - o_q                                   # q | k | v are consecutive columns of the product
+        qkv = torch.empty((T, nq), dtype=torch.float32, device=dev)
+        S.check(lib.b2l_seq_cast_f32(_p(proj, o_q), ld, _p(qkv), nq, T, nq, ctx.act, ctx.stream), "b2l_seq_cast_f32")
+        _scan(ctx, q=_p(qkv), ldq=nq, k=_p(qkv, o_k - o_q), ldk=nq, v=_p(qkv, o_v - o_q), ldv=nq, q_mult=self.K ** -0.5, decay=_p(alpha),
               ldd=n, per_channel=True, state=ctx.state[self.name + ".S"], out=_p(o), ldo=self.H * self.V, heads=self.H, qk_heads=self.H,
               K=self.K, V=self.V)
         S.check(lib.b2l_seq_group_norm_gate(_p(o), self.H * self.V, _p(self.w_norm), 1, _p(proj, o_g), ld, S.ACT_SILU, 0, self.eps, float(out_mult),
