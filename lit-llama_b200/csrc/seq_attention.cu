@@ -7,7 +7,7 @@
 // attention kernel (a second kernel in the same call), so a portion longer than a block cannot overwrite what it
 // still has to read.
 //
-// attention kernel: WPQ warps per (query, head).  A warp takes batches of 32 consecutive keys: each lane scores one
+// warp kernel (single tokens, and shapes the tiled kernel does not take): WPQ warps per (query, head).  A warp takes batches of 32 consecutive keys: each lane scores one
 // key (q from shared memory, its key row by 16-byte loads), the batch maximum and the weights go through shuffles,
 // and the value rows are accumulated with lanes over value channels.  Scores, weights and accumulators are f32.
 #include "seq_common.cuh"
@@ -21,20 +21,21 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ q, const act_
 
 template <>
 __device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* __restrict__ q, const __nv_bfloat16* __restrict__ k, int K, bool vec) {
-  float s0 = 0.f, s1 = 0.f;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
   if (vec) {
+#pragma unroll 4
     for (int i = 0; i < K; i += 8) {
       const uint4 w = *reinterpret_cast<const uint4*>(k + i);
       const float4 qa = *reinterpret_cast<const float4*>(q + i), qb = *reinterpret_cast<const float4*>(q + i + 4);
       s0 = fmaf(__uint_as_float(w.x << 16), qa.x, s0); s1 = fmaf(__uint_as_float(w.x & 0xffff0000u), qa.y, s1);
-      s0 = fmaf(__uint_as_float(w.y << 16), qa.z, s0); s1 = fmaf(__uint_as_float(w.y & 0xffff0000u), qa.w, s1);
+      s2 = fmaf(__uint_as_float(w.y << 16), qa.z, s2); s3 = fmaf(__uint_as_float(w.y & 0xffff0000u), qa.w, s3);
       s0 = fmaf(__uint_as_float(w.z << 16), qb.x, s0); s1 = fmaf(__uint_as_float(w.z & 0xffff0000u), qb.y, s1);
-      s0 = fmaf(__uint_as_float(w.w << 16), qb.z, s0); s1 = fmaf(__uint_as_float(w.w & 0xffff0000u), qb.w, s1);
+      s2 = fmaf(__uint_as_float(w.w << 16), qb.z, s2); s3 = fmaf(__uint_as_float(w.w & 0xffff0000u), qb.w, s3);
     }
   } else {
     for (int i = 0; i < K; ++i) s0 = fmaf(__bfloat162float(k[i]), q[i], s0);
   }
-  return s0 + s1;
+  return (s0 + s1) + (s2 + s3);
 }
 
 template <>
@@ -53,13 +54,14 @@ __device__ __forceinline__ float dot_row<float>(const float* __restrict__ q, con
 }
 
 template <typename act_t, int WPQ>
-__global__ void __launch_bounds__(128) seq_block_attention_kernel(b2l_seq_attn_args a, int vec) {
+__global__ void __launch_bounds__(WPQ > 4 ? 32 * WPQ : 128) seq_block_attention_kernel(b2l_seq_attn_args a, int vec) {
   extern __shared__ float smem[];
-  constexpr int QPC = 4 / WPQ;                       // (query, head) pairs per CTA
+  constexpr int NW = WPQ > 4 ? WPQ : 4;              // warps per CTA
+  constexpr int QPC = NW / WPQ;                      // (query, head) pairs per CTA
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int K = a.K, V = a.V, Kpad = (K + 3) & ~3;
   float* sq = smem;                                  // [QPC][Kpad]
-  float* sm = sq + QPC * Kpad;                       // merge area [4][2 + V]
+  float* sm = sq + QPC * Kpad;                       // merge area [NW][2 + 32 * ATT_VMAX]
 
   const int pair = blockIdx.x * QPC + warp / WPQ, sub = warp % WPQ;
   const bool live = pair < a.T * a.heads;
@@ -101,9 +103,10 @@ __global__ void __launch_bounds__(128) seq_block_attention_kernel(b2l_seq_attn_a
       for (int c = 0; c < ATT_VMAX; ++c) acc[c] *= (m == -INFINITY ? 0.f : corr);
       m = mn;
       const int nb = min(32, p - jb + 1);
-      for (int jj = 0; jj < nb; ++jj) {
-        const float wj = __shfl_sync(0xffffffffu, w, jj);
-        const int jv = jb + jj;
+#pragma unroll 8
+      for (int jj = 0; jj < 32; ++jj) {
+        const float wj = __shfl_sync(0xffffffffu, w, jj);      // 0 beyond the last key of the batch
+        const int jv = jb + min(jj, nb - 1);                    // a valid row for the masked tail (weight 0)
         const act_t* vr = jv >= pos0 ? vn + (size_t)(jv - pos0) * a.ldv + (size_t)g * V
                                      : cv + ((size_t)(jv - c0) * a.kv_heads + g) * V;
 #pragma unroll
@@ -361,8 +364,8 @@ extern "C" int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t 
   const int vec = ((a->K * esz) % 16 == 0) && (((uintptr_t)a->k_new | (uintptr_t)a->cache_k) % 16 == 0) && (a->K % 8 == 0 || esz == 4);
   const int pairs = a->T * a->heads;
   const int Kpad = (a->K + 3) & ~3;
-  const bool split = pairs < 2 * sm_count();          // few queries (decoding): four warps share one query's keys
-  const size_t smem = sizeof(float) * ((size_t)(split ? 1 : 4) * Kpad + 4 * (2 + ATT_VMAX * 32));
+  const bool split = pairs < 2 * sm_count();          // few queries (decoding): sixteen warps share one query's keys
+  const size_t smem = sizeof(float) * ((size_t)(split ? 1 : 4) * Kpad + (split ? 16 : 4) * (2 + ATT_VMAX * 32));
   B2L_CHECK_SUPPORTED(smem <= 48 * 1024, "b2l_seq_block_attention: key size %d too large", a->K);
   const bool al = (((uintptr_t)a->q | (uintptr_t)a->k_new | (uintptr_t)a->v_new | (uintptr_t)a->cache_k | (uintptr_t)a->cache_v) % 16) == 0;
   const size_t tile_smem = sizeof(float) * ((size_t)(TQ + TK) * (a->K + 4) + (size_t)TK * a->V + (size_t)TQ * (TK + 1));
@@ -378,10 +381,10 @@ extern "C" int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t 
          : vc == 3 ? launch_tile<float, 3>(a, s, 6) : launch_tile<float, 4>(a, s, 7);
     if (rc) return rc;
   } else if (a->act_dtype == B2L_BF16) {
-    if (split) seq_block_attention_kernel<__nv_bfloat16, 4><<<pairs, 128, smem, s>>>(*a, vec);
+    if (split) seq_block_attention_kernel<__nv_bfloat16, 16><<<pairs, 512, smem, s>>>(*a, vec);
     else seq_block_attention_kernel<__nv_bfloat16, 1><<<(pairs + 3) / 4, 128, smem, s>>>(*a, vec);
   } else {
-    if (split) seq_block_attention_kernel<float, 4><<<pairs, 128, smem, s>>>(*a, vec);
+    if (split) seq_block_attention_kernel<float, 16><<<pairs, 512, smem, s>>>(*a, vec);
     else seq_block_attention_kernel<float, 1><<<(pairs + 3) / 4, 128, smem, s>>>(*a, vec);
   }
   B2L_LAUNCH_CHECK("seq_block_attention_kernel");

@@ -59,6 +59,49 @@ __global__ void __launch_bounds__(256) seq_norm_add_norm_kernel(const act_t* __r
   for (int i = threadIdx.x; i < D; i += blockDim.x) st_act(hr, i, xr[i] * r2 * ld_act(wn, i));   // own writes: visible to this thread
 }
 
+// The same with the row held in registers (D <= 256 * EPT): every operand is requested before the first reduction, so
+// a single-token step pays one memory latency instead of three.
+template <typename act_t, int EPT>
+__global__ void __launch_bounds__(256) seq_norm_add_norm_reg_kernel(const act_t* __restrict__ y, const act_t* __restrict__ wp, float eps,
+                                                                    float* __restrict__ x, const act_t* __restrict__ wn,
+                                                                    act_t* __restrict__ h, int D) {
+  __shared__ float red[32];
+  const act_t* yr = y + (size_t)blockIdx.x * D;
+  float* xr = x + (size_t)blockIdx.x * D;
+  float yv[EPT], xv[EPT], pv[EPT], nv[EPT];
+#pragma unroll
+  for (int e = 0; e < EPT; ++e) {
+    const int i = threadIdx.x + e * 256;
+    const bool in = i < D;
+    yv[e] = in ? ld_act(yr, i) : 0.f;
+    xv[e] = in ? xr[i] : 0.f;
+    pv[e] = in ? ld_act(wp, i) : 0.f;
+    nv[e] = (in && wn) ? ld_act(wn, i) : 0.f;
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < EPT; ++e) ss += yv[e] * yv[e];
+  ss = block_sum(ss, red);
+  const float rinv = 1.0f / sqrtf(ss / (float)D + eps);
+  float s2 = 0.f;
+#pragma unroll
+  for (int e = 0; e < EPT; ++e) {
+    const int i = threadIdx.x + e * 256;
+    xv[e] += yv[e] * rinv * pv[e];
+    if (i < D) xr[i] = xv[e];
+    s2 += xv[e] * xv[e];
+  }
+  if (wn == nullptr) return;
+  s2 = block_sum(s2, red);
+  const float r2 = 1.0f / sqrtf(s2 / (float)D + eps);
+  act_t* hr = h + (size_t)blockIdx.x * D;
+#pragma unroll
+  for (int e = 0; e < EPT; ++e) {
+    const int i = threadIdx.x + e * 256;
+    if (i < D) st_act(hr, i, xv[e] * r2 * nv[e]);
+  }
+}
+
 template <typename act_t>
 __global__ void seq_gated_act_kernel(const act_t* __restrict__ gu, int ldgu, act_t* __restrict__ out, int F, int act) {
   const act_t* g = gu + (size_t)blockIdx.x * ldgu;
@@ -206,6 +249,38 @@ __global__ void seq_group_norm_gate_kernel(const float* __restrict__ o, int ldo,
   }
 }
 
+// The same for large groups (a whole layer's channels normalised together): one CTA per (token, group).
+template <typename act_t>
+__global__ void __launch_bounds__(256) seq_group_norm_gate_block_kernel(const float* __restrict__ o, int ldo, const act_t* __restrict__ w, int w_shared,
+                                                                        const act_t* __restrict__ gate, int ldg, int gate_act, int gate_first,
+                                                                        float eps, float out_mult, act_t* __restrict__ out, int ldout, int groups,
+                                                                        int group) {
+  __shared__ float red[32];
+  const int t = blockIdx.x / groups, g = blockIdx.x % groups;
+  const float* p = o + (size_t)t * ldo + (size_t)g * group;
+  const act_t* gp = gate ? gate + (size_t)t * ldg + (size_t)g * group : nullptr;
+  auto gate_of = [&](int i) {
+    const float z = ld_act(gp, i);
+    return gate_act == B2L_SEQ_ACT_SILU ? silu_f(z) : (gate_act == B2L_SEQ_ACT_SIGMOID ? sigmoid_f(z) : gelu_tanh_f(z));
+  };
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < group; i += blockDim.x) {
+    float v = p[i];
+    if (gp && gate_first) v *= gate_of(i);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float r = out_mult / sqrtf(ss / (float)group + eps);
+  act_t* q = out + (size_t)t * ldout + (size_t)g * group;
+  for (int i = threadIdx.x; i < group; i += blockDim.x) {
+    float v = p[i];
+    if (gp && gate_first) v *= gate_of(i);
+    v = v * r * ld_act(w, w_shared ? i : g * group + i);
+    if (gp && !gate_first) v *= gate_of(i);
+    st_act(q, i, v);
+  }
+}
+
 // Per-head RMS norm + partial rotation.  One warp per (token, head).
 template <typename act_t, typename out_t>
 __global__ void seq_headnorm_rope_kernel(const act_t* __restrict__ x, int ldx, const act_t* __restrict__ w, float eps,
@@ -276,8 +351,15 @@ extern "C" int b2l_seq_norm_add_norm(const void* y, const void* w_post, float ep
   B2L_CHECK_ARG((w_next == nullptr) == (h == nullptr), "b2l_seq_norm_add_norm: w_next and h go together");
   B2L_CHECK_ARG(T >= 0 && D > 0, "b2l_seq_norm_add_norm: bad size");
   if (T == 0) return 0;
-  B2L_SEQ_DISPATCH(act_dtype, (seq_norm_add_norm_kernel<act_t><<<T, 256, 0, (cudaStream_t)stream>>>(
-                                  (const act_t*)y, (const act_t*)w_post, eps, x, (const act_t*)w_next, (act_t*)h, D)));
+#define B2L_NAN_ARGS (const act_t*)y, (const act_t*)w_post, eps, x, (const act_t*)w_next, (act_t*)h, D
+  B2L_SEQ_DISPATCH(act_dtype, {
+    cudaStream_t s_ = (cudaStream_t)stream;
+    if (D <= 1024) seq_norm_add_norm_reg_kernel<act_t, 4><<<T, 256, 0, s_>>>(B2L_NAN_ARGS);
+    else if (D <= 2048) seq_norm_add_norm_reg_kernel<act_t, 8><<<T, 256, 0, s_>>>(B2L_NAN_ARGS);
+    else if (D <= 4096) seq_norm_add_norm_reg_kernel<act_t, 16><<<T, 256, 0, s_>>>(B2L_NAN_ARGS);
+    else seq_norm_add_norm_kernel<act_t><<<T, 256, 0, s_>>>(B2L_NAN_ARGS);
+  });
+#undef B2L_NAN_ARGS
   B2L_LAUNCH_CHECK("seq_norm_add_norm_kernel");
   return 0;
 }
@@ -354,9 +436,14 @@ extern "C" int b2l_seq_group_norm_gate(const float* o, int ldo, const void* w, i
   B2L_CHECK_ARG(T >= 0 && n > 0 && group > 0 && n % group == 0 && ldo >= n && ldout >= n, "b2l_seq_group_norm_gate: bad size");
   if (T == 0) return 0;
   const int ids = T * (n / group);
-  B2L_SEQ_DISPATCH(act_dtype, (seq_group_norm_gate_kernel<act_t><<<(ids + 3) / 4, 128, 0, (cudaStream_t)stream>>>(
-                                  o, ldo, (const act_t*)w, w_shared, (const act_t*)gate, ldg, gate_act, gate_first, eps, out_mult,
-                                  (act_t*)out, ldout, T, n / group, group)));
+  B2L_SEQ_DISPATCH(act_dtype, {
+    if (group >= 512)
+      seq_group_norm_gate_block_kernel<act_t><<<ids, 256, 0, (cudaStream_t)stream>>>(
+          o, ldo, (const act_t*)w, w_shared, (const act_t*)gate, ldg, gate_act, gate_first, eps, out_mult, (act_t*)out, ldout, n / group, group);
+    else
+      seq_group_norm_gate_kernel<act_t><<<(ids + 3) / 4, 128, 0, (cudaStream_t)stream>>>(
+          o, ldo, (const act_t*)w, w_shared, (const act_t*)gate, ldg, gate_act, gate_first, eps, out_mult, (act_t*)out, ldout, T, n / group, group);
+  });
   B2L_LAUNCH_CHECK("seq_group_norm_gate_kernel");
   return 0;
 }

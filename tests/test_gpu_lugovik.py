@@ -412,6 +412,36 @@ def test_head_norm_and_rotation(rot):
     assert rel(out.view(T, H, K), want) < 2e-5     # f32 angles at position ~1000
 
 
+@pytest.mark.parametrize("D", [50, 1030, 2048, 3000, 5000])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_post_norm_residual_pre_norm_all_widths(D, dtype):
+    _, S, M = _pkg()
+    T = 3
+    ctx = _ctx(T, dtype=dtype)
+    x, y, w1, w2 = torch.randn(T, D), (torch.randn(T, D) * 3).to(dtype), (torch.rand(D) + 0.5).to(dtype), (torch.rand(D) + 0.5).to(dtype)
+    for nxt in (True, False):
+        dx, h = dev(x.clone()), torch.zeros(T, D, device=DEV, dtype=dtype)
+        S.check(S.lib().b2l_seq_norm_add_norm(M._p(dev(y)), M._p(dev(w1)), 1e-5, M._p(dx), M._p(dev(w2)) if nxt else None, M._p(h) if nxt else None, T, D,
+                                              ctx.act, ctx.stream), "nan")
+        x2 = x.double() + O.rms_norm(y.double(), w1.double(), 1e-5)
+        assert rel(dx, x2) < 1e-6
+        if nxt:
+            assert rel(h, O.rms_norm(x2, w2.double(), 1e-5)) < (1e-6 if dtype == torch.float32 else 4e-3)
+
+
+@pytest.mark.parametrize("group,n", [(12, 48), (512, 1024), (2000, 2000)])
+def test_grouped_read_out_norm_small_and_large_groups(group, n):
+    _, S, M = _pkg()
+    T = 4
+    ctx = _ctx(T)
+    o, gate, wn = torch.randn(T, n), torch.randn(T, n), torch.rand(n) + 0.5
+    res = torch.empty(T, n, device=DEV)
+    S.check(S.lib().b2l_seq_group_norm_gate(M._p(dev(o)), n, M._p(dev(wn)), 0, M._p(dev(gate)), n, S.ACT_SILU, 1, 1e-5, 0.5, M._p(res), n, T, n, group, ctx.act,
+                                            ctx.stream), "gng")
+    ref = O.rms_norm((o.double() * O.silu(gate.double())).view(T, n // group, group), None, 1e-5).reshape(T, n) * wn.double() * 0.5
+    assert rel(res, ref) < 1e-6
+
+
 def test_row_kernels():
     """Embedding scale, RMS norm with row selection, post-norm + residual + next pre-norm, gated activation, grouped
     read-out norm with its gate in both orders, both decay forms (including arguments where exp or sigmoid saturate)."""
