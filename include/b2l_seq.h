@@ -84,7 +84,13 @@ typedef struct {
   float* state; const int* meta;
   float* out; int ldo;
   int T, heads, qk_heads, K, V, act_dtype;
+  /* Without the delta rule a long portion may be cut into n_chunks (> 1) chunks that run in parallel: every chunk's
+   * local end state and total decay first, a short combine that gives every chunk its start state, then the outputs.
+   * work_state: f32 [n_chunks][heads][V][K]; work_decay: f32 [n_chunks][heads][K] (per-channel decay) or
+   * [n_chunks][heads].  b2l_seq_scan_chunks() says how many chunks a portion of T tokens wants (1 = sequential). */
+  float* work_state; float* work_decay; int n_chunks;
 } b2l_seq_scan_args;
+int b2l_seq_scan_chunks(int T, int delta);
 int b2l_seq_scan(const b2l_seq_scan_args* a, b2l_stream_t stream);
 
 /* Read-out of a recurrence: groups of `group` consecutive channels of o (f32 [T, n]) are divided by their root

@@ -27,6 +27,7 @@ class ScanArgs(C.Structure):
         ("state", c_void_p), ("meta", c_void_p),
         ("out", c_void_p), ("ldo", c_int),
         ("T", c_int), ("heads", c_int), ("qk_heads", c_int), ("K", c_int), ("V", c_int), ("act_dtype", c_int),
+        ("work_state", c_void_p), ("work_decay", c_void_p), ("n_chunks", c_int),
     ]
 
 
@@ -58,6 +59,7 @@ _SIGS = {
     "b2l_seq_decay": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                               c_void_p]),
     "b2l_seq_scan": (c_int, [C.POINTER(ScanArgs), c_void_p]),
+    "b2l_seq_scan_chunks": (c_int, [c_int, c_int]),
     "b2l_seq_group_norm_gate": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "b2l_seq_headnorm_rope": (c_int, [c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_int,

@@ -26,8 +26,10 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // Inputs of SCAN_TC steps go to shared memory with cp.async, two stages deep: stage s+1 is in flight while the
 // recurrence runs over stage s, so the sequential loop never waits on global memory after the first stage.
 // Stage layout: q[TC][KP] k[TC][KP] d[TC][DP] v[TC][cols] vs[TC] beta[TC] (+ 2*TC unused: stages stay 16-byte aligned).
-template <int DELTA, typename act_t>
-__global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_args a, int R, int vec) {
+// PASS 0: the recurrence with outputs, from the slot's state (one chunk) or from a chunk's start state in the workspace.
+// PASS 1: a chunk's local end state from zero and its total decay, no outputs (first pass of a chunked portion).
+template <int DELTA, typename act_t, int PASS>
+__global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_args a, int R, int vec, int chunk_len) {
   extern __shared__ __align__(16) float smem[];
   const int KP = R * SCAN_KPT;                 // padded key size
   const int cols = SCAN_THREADS / R;           // value columns of this CTA
@@ -41,7 +43,10 @@ __global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_arg
   const int v0 = blockIdx.x * cols, vcol = v0 + cidx;
   const int K = a.K, V = a.V;
   const int slot = a.meta[0];
-  float* st = a.state + ((size_t)slot * a.heads + h) * (size_t)V * K;
+  const bool chunked = a.n_chunks > 1;
+  const int t_begin = blockIdx.z * chunk_len, t_end = min(a.T, t_begin + chunk_len);
+  float* st = chunked ? a.work_state + ((size_t)blockIdx.z * a.heads + h) * (size_t)V * K
+                      : a.state + ((size_t)slot * a.heads + h) * (size_t)V * K;
   const float skip = a.skip ? ld_act((const act_t*)a.skip, h) : 0.f;
   const float* gq = a.q + (size_t)hq * K;
   const float* gk = a.k + (size_t)hq * K;
@@ -69,7 +74,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_arg
   }
 
   auto prefetch = [&](int t0, int b) {
-    const int nt = min(SCAN_TC, a.T - t0);
+    const int nt = min(SCAN_TC, t_end - t0);
     float* sq = smem + b * stage;
     float* sk = sq + SCAN_TC * KP;
     float* sd = sk + SCAN_TC * KP;
@@ -102,24 +107,27 @@ __global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_arg
     cp_async_commit();
   };
   auto beta_of = [&](int t0) -> float {   // raw gate of step t0 + tid: act-typed, so a plain load kept in a register
-    return (DELTA && tid < min(SCAN_TC, a.T - t0)) ? ld_act((const act_t*)a.beta, (size_t)(t0 + tid) * a.ldb + h) : 0.f;
+    return (DELTA && tid < min(SCAN_TC, t_end - t0)) ? ld_act((const act_t*)a.beta, (size_t)(t0 + tid) * a.ldb + h) : 0.f;
   };
 
   float S[SCAN_KPT];
 #pragma unroll
   for (int i = 0; i < SCAN_KPT; ++i) {
     const int kk = ((i >> 2) * R + r) * 4 + (i & 3);
-    S[i] = (kk < K && vcol < V) ? st[(size_t)vcol * K + kk] : 0.f;
+    S[i] = (PASS == 0 && kk < K && vcol < V) ? st[(size_t)vcol * K + kk] : 0.f;
   }
+  float P[PASS ? SCAN_KPT : 1];       // PASS 1: the chunk's total decay of this lane's key channels
+#pragma unroll
+  for (int i = 0; i < (PASS ? SCAN_KPT : 1); ++i) P[i] = 1.f;
 
   __syncthreads();                    // the padding is written before any copy lands next to it
-  prefetch(0, 0);
-  if (DELTA && tid < SCAN_TC) smem[beta_at + tid] = sigmoid_f(beta_of(0));
+  prefetch(t_begin, 0);
+  if (DELTA && tid < SCAN_TC) smem[beta_at + tid] = sigmoid_f(beta_of(t_begin));
 
   int b = 0;
-  for (int t0 = 0; t0 < a.T; t0 += SCAN_TC, b ^= 1) {
-    const int nt = min(SCAN_TC, a.T - t0);
-    const bool more = t0 + SCAN_TC < a.T;
+  for (int t0 = t_begin; t0 < t_end; t0 += SCAN_TC, b ^= 1) {
+    const int nt = min(SCAN_TC, t_end - t0);
+    const bool more = t0 + SCAN_TC < t_end;
     float beta_next = 0.f;
     if (more) {
       prefetch(t0 + SCAN_TC, b ^ 1);
@@ -152,11 +160,13 @@ __global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_arg
         for (int i4 = 0; i4 < SCAN_KPT / 4; ++i4) {
           const float4 dv = d4[i4 * R + r];
           S[i4 * 4 + 0] *= dv.x; S[i4 * 4 + 1] *= dv.y; S[i4 * 4 + 2] *= dv.z; S[i4 * 4 + 3] *= dv.w;
+          if (PASS) { P[i4 * 4 + 0] *= dv.x; P[i4 * 4 + 1] *= dv.y; P[i4 * 4 + 2] *= dv.z; P[i4 * 4 + 3] *= dv.w; }
         }
       } else {
         const float d = sd[t];
 #pragma unroll
         for (int i = 0; i < SCAN_KPT; ++i) S[i] *= d;
+        if (PASS) P[0] *= d;
       }
       const float vraw = sv[t * cols + cidx];
       float u = vraw * svs[t];
@@ -171,6 +181,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_arg
         for (int o = 1; o < R; o <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
         u = sb[t] * (u - p);
       }
+      if (PASS) {
+#pragma unroll
+        for (int i = 0; i < SCAN_KPT; ++i) S[i] = fmaf(kr[i], u, S[i]);
+        continue;
+      }
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
       for (int i = 0; i < SCAN_KPT; i += 4) {
@@ -184,25 +199,64 @@ __global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_arg
       if (r == 0) so[t * cols + cidx] = o * a.q_mult + skip * vraw;
     }
     __syncthreads();
-    for (int i = tid; i < nt * ncol; i += SCAN_THREADS) {
-      const int t = i / ncol, c = i - t * ncol;
-      a.out[(size_t)(t0 + t) * a.ldo + (size_t)h * V + v0 + c] = so[t * cols + c];
+    if (PASS == 0) {
+      for (int i = tid; i < nt * ncol; i += SCAN_THREADS) {
+        const int t = i / ncol, c = i - t * ncol;
+        a.out[(size_t)(t0 + t) * a.ldo + (size_t)h * V + v0 + c] = so[t * cols + c];
+      }
     }
     if (DELTA && more && tid < SCAN_TC) smem[(b ^ 1) * stage + beta_at + tid] = sigmoid_f(beta_next);
   }
 
+  if (PASS == 0 && chunked) return;   // chunk outputs: the slot's state is written by the combine kernel
 #pragma unroll
   for (int i = 0; i < SCAN_KPT; ++i) {
     const int kk = ((i >> 2) * R + r) * 4 + (i & 3);
     if (kk < K && vcol < V) st[(size_t)vcol * K + kk] = S[i];
   }
+  if (PASS && blockIdx.x == 0 && cidx == 0) {
+    float* wd = a.work_decay + ((size_t)blockIdx.z * a.heads + h) * (a.decay_per_channel ? K : 1);
+    if (a.decay_per_channel) {
+#pragma unroll
+      for (int i = 0; i < SCAN_KPT; ++i) {
+        const int kk = ((i >> 2) * R + r) * 4 + (i & 3);
+        if (kk < K) wd[kk] = P[i];
+      }
+    } else if (r == 0) {
+      wd[0] = P[0];
+    }
+  }
 }
 
-static DynSmemCache g_scan_smem[4];
+// Between the passes of a chunked portion: work_state[c] (a chunk's local end state) becomes the chunk's START state,
+// s_0 = the slot's state, s_(c+1) = D_c s_c + local_c, and the slot's state becomes s_n.  One thread per state entry.
+__global__ void seq_scan_combine_kernel(b2l_seq_scan_args a) {
+  const size_t per_head = (size_t)a.V * a.K, n = (size_t)a.heads * per_head;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int h = (int)(i / per_head), kk = (int)(i % a.K);
+  float* st = a.state + (size_t)a.meta[0] * n;
+  float s = st[i];
+  for (int c = 0; c < a.n_chunks; ++c) {
+    const float d = a.work_decay[((size_t)c * a.heads + h) * (a.decay_per_channel ? a.K : 1) + (a.decay_per_channel ? kk : 0)];
+    const float local = a.work_state[(size_t)c * n + i];
+    a.work_state[(size_t)c * n + i] = s;
+    s = fmaf(d, s, local);
+  }
+  st[i] = s;
+}
+
+static DynSmemCache g_scan_smem[6];
+constexpr int SCAN_CHUNK = 128;      // tokens per chunk of a chunked portion (a multiple of SCAN_TC)
 
 }  // namespace b2l
 
 using namespace b2l;
+
+extern "C" int b2l_seq_scan_chunks(int T, int delta) {
+  if (delta || T < 2 * SCAN_CHUNK) return 1;
+  return (T + SCAN_CHUNK - 1) / SCAN_CHUNK;
+}
 
 extern "C" int b2l_seq_scan(const b2l_seq_scan_args* a, b2l_stream_t stream) {
   B2L_CHECK_ARG(a != nullptr, "b2l_seq_scan: null argument block");
@@ -211,7 +265,11 @@ extern "C" int b2l_seq_scan(const b2l_seq_scan_args* a, b2l_stream_t stream) {
   B2L_CHECK_ARG(a->T >= 0 && a->heads > 0 && a->qk_heads > 0 && a->K > 0 && a->V > 0, "b2l_seq_scan: bad size");
   B2L_CHECK_ARG(a->heads % a->qk_heads == 0, "b2l_seq_scan: heads %d not a multiple of qk_heads %d", a->heads, a->qk_heads);
   B2L_CHECK_SUPPORTED(a->K <= 32 * SCAN_KPT, "b2l_seq_scan: key size %d above %d", a->K, 32 * SCAN_KPT);
+  B2L_CHECK_ARG(a->n_chunks <= 1 || (!a->delta && a->work_state && a->work_decay && a->n_chunks == (a->T + SCAN_CHUNK - 1) / SCAN_CHUNK),
+                "b2l_seq_scan: chunked portions need the workspace, no delta rule and n_chunks from b2l_seq_scan_chunks");
   if (a->T == 0) return 0;
+  const int n_chunks = a->n_chunks > 1 ? a->n_chunks : 1;
+  const int chunk_len = n_chunks > 1 ? SCAN_CHUNK : a->T;
   int R = 1;
   while (R * SCAN_KPT < a->K) R <<= 1;
   const int KP = R * SCAN_KPT, cols = SCAN_THREADS / R;
@@ -219,18 +277,26 @@ extern "C" int b2l_seq_scan(const b2l_seq_scan_args* a, b2l_stream_t stream) {
   auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
   const int vec = a->K % 4 == 0 && a->ldq % 4 == 0 && a->ldk % 4 == 0 && al16(a->q) && al16(a->k) &&
                   (!a->decay_per_channel || (a->ldd % 4 == 0 && al16(a->decay)));
-  dim3 grid((unsigned)((a->V + cols - 1) / cols), (unsigned)a->heads);
+  dim3 grid((unsigned)((a->V + cols - 1) / cols), (unsigned)a->heads, (unsigned)n_chunks);
   cudaStream_t s = (cudaStream_t)stream;
-#define B2L_SCAN_LAUNCH(D, T_, slot_)                                                     \
+#define B2L_SCAN_LAUNCH(D, T_, P_, slot_)                                                 \
   do {                                                                                    \
-    int rc_ = ensure_dyn_smem(seq_scan_kernel<D, T_>, smem, g_scan_smem[slot_]);          \
+    int rc_ = ensure_dyn_smem(seq_scan_kernel<D, T_, P_>, smem, g_scan_smem[slot_]);      \
     if (rc_) return rc_;                                                                  \
-    seq_scan_kernel<D, T_><<<grid, SCAN_THREADS, smem, s>>>(*a, R, vec);                      \
+    seq_scan_kernel<D, T_, P_><<<grid, SCAN_THREADS, smem, s>>>(*a, R, vec, chunk_len);   \
   } while (0)
+  if (n_chunks > 1) {   // local end states, combine, then the outputs below start from the workspace
+    if (a->act_dtype == B2L_BF16) B2L_SCAN_LAUNCH(0, __nv_bfloat16, 1, 4);
+    else if (a->act_dtype == B2L_F32) B2L_SCAN_LAUNCH(0, float, 1, 5);
+    B2L_LAUNCH_CHECK("seq_scan_kernel (local states)");
+    const size_t n = (size_t)a->heads * a->V * a->K;
+    seq_scan_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(*a);
+    B2L_LAUNCH_CHECK("seq_scan_combine_kernel");
+  }
   if (a->act_dtype == B2L_BF16) {
-    if (a->delta) B2L_SCAN_LAUNCH(1, __nv_bfloat16, 0); else B2L_SCAN_LAUNCH(0, __nv_bfloat16, 1);
+    if (a->delta) B2L_SCAN_LAUNCH(1, __nv_bfloat16, 0, 0); else B2L_SCAN_LAUNCH(0, __nv_bfloat16, 0, 1);
   } else if (a->act_dtype == B2L_F32) {
-    if (a->delta) B2L_SCAN_LAUNCH(1, float, 2); else B2L_SCAN_LAUNCH(0, float, 3);
+    if (a->delta) B2L_SCAN_LAUNCH(1, float, 0, 2); else B2L_SCAN_LAUNCH(0, float, 0, 3);
   } else {
     set_error("b2l_seq_scan: act_dtype %d unsupported", a->act_dtype);
     return B2L_E_UNSUPPORTED;

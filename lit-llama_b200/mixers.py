@@ -90,11 +90,17 @@ class GatedMLP:
 # ------------------------------------------------------------------------------------------------ recurrences
 def _scan(ctx: StepContext, *, q, ldq, k, ldk, v, ldv, q_mult, decay, ldd, per_channel, state, out, ldo, heads, qk_heads,
           K, V, beta=None, ldb=0, vscale=None, ldvs=0, skip=None) -> None:
+    lib = S.lib()
+    n_chunks = lib.b2l_seq_scan_chunks(ctx.T, int(beta is not None))
+    ws = wd = None
+    if n_chunks > 1:      # long portion, no delta rule: chunks in parallel (local states, combine, outputs)
+        ws = torch.empty((n_chunks, heads, V, K), dtype=torch.float32, device=state.device)
+        wd = torch.empty((n_chunks, heads, K if per_channel else 1), dtype=torch.float32, device=state.device)
     a = S.ScanArgs(q=q, ldq=ldq, k=k, ldk=ldk, v=v, ldv=ldv, q_mult=float(q_mult), decay=decay, ldd=ldd,
                    decay_per_channel=int(per_channel), beta=beta, ldb=ldb, delta=int(beta is not None), vscale=vscale, ldvs=ldvs,
                    skip=skip, state=_p(state), meta=_p(ctx.meta), out=out, ldo=ldo, T=ctx.T, heads=heads, qk_heads=qk_heads, K=K, V=V,
-                   act_dtype=ctx.act)
-    S.check(S.lib().b2l_seq_scan(C.byref(a), ctx.stream), "b2l_seq_scan")
+                   act_dtype=ctx.act, work_state=_p(ws), work_decay=_p(wd), n_chunks=n_chunks)
+    S.check(lib.b2l_seq_scan(C.byref(a), ctx.stream), "b2l_seq_scan")
 
 
 class ChannelDeltaMixer:

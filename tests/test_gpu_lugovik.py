@@ -175,6 +175,19 @@ def test_interleaved_requests_and_reused_slots():
     assert engine.pool.reused > before and engine.pool.free_slots() == 3
 
 
+def test_a_long_prompt_in_one_portion_and_in_pieces():
+    """600 tokens: the recurrences without the delta rule take the chunk-parallel path in the whole-prompt run and
+    the sequential one in the small portions; both match the plain model."""
+    cfg = cfg_a()
+    engine, W = build(cfg, torch.float32)
+    toks = tokens_for(cfg, 600, seed=8)
+    want = O.forward(cfg, W, toks)
+    whole = run_schedule(engine, "w", toks, [600])
+    parts = run_schedule(engine, "p", toks, cuts_of(600, [100, 3, 270, 1]))
+    assert rel(whole, parts) < 2e-5
+    assert max(rel(whole[t], want[t]) for t in range(0, 600, 7)) < 4 * F32_TOL
+
+
 def test_long_decoding_across_many_blocks():
     cfg = cfg_b()                      # block of 5 positions: 120 decoded tokens pass 24 block edges
     engine, W = build(cfg, torch.float32)
@@ -289,6 +302,25 @@ def test_decayed_outer_product_scan_alone(K, V, H, G, per_channel):
     state = torch.zeros(1, H, V, K, device=DEV)
     got = _scan_call(q.to(DEV), k.to(DEV), v.to(DEV), a.to(DEV).contiguous(), state, vscale=dt.to(DEV), skip=D.to(DEV), qk_heads=G, q_mult=0.5)
     assert rel(got, want) < 2e-5
+
+
+@pytest.mark.parametrize("K,V,H,per_channel", [(24, 40, 2, True), (128, 64, 3, False), (7, 5, 1, True)])
+def test_long_portions_run_in_parallel_chunks_and_carry_the_state(K, V, H, per_channel):
+    """Portions of 256 tokens or more (no delta rule) are cut into chunks that run in parallel; the result and the
+    carried state equal the token-by-token recurrence, also when a chunked portion follows another portion."""
+    _, S, _ = _pkg()
+    T = 700
+    assert S.lib().b2l_seq_scan_chunks(300, 0) > 1 and S.lib().b2l_seq_scan_chunks(300, 1) == 1 and S.lib().b2l_seq_scan_chunks(255, 0) == 1
+    q, k, v = torch.randn(T, H, K), torch.randn(T, H, K) * 0.3, torch.randn(T, H, V)
+    a = torch.rand(T, H, K) * 0.2 + 0.8 if per_channel else torch.rand(T, H) * 0.2 + 0.8
+    want = torch.stack([O.decayed_outer_head(q[:, h].double(), k[:, h].double(), v[:, h].double(), a[:, h].double()) for h in range(H)], dim=1)
+    for cuts in ([T], [300, 400], [1, 699], [37, 263, 1, 399]):
+        state = torch.zeros(1, H, V, K, device=DEV)
+        outs, at = [], 0
+        for c in cuts:
+            outs.append(_scan_call(dev(q[at:at + c]), dev(k[at:at + c]), dev(v[at:at + c]), dev(a[at:at + c]), state))
+            at += c
+        assert rel(torch.cat(outs), want) < 2e-5, cuts
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
