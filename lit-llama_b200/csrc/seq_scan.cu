@@ -29,7 +29,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // PASS 0: the recurrence with outputs, from the slot's state (one chunk) or from a chunk's start state in the workspace.
 // PASS 1: a chunk's local end state from zero and its total decay, no outputs (first pass of a chunked portion).
 template <int DELTA, typename act_t, int PASS>
-__global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_args a, int R, int vec, int chunk_len) {
+__global__ void __launch_bounds__(SCAN_THREADS, 2) seq_scan_kernel(b2l_seq_scan_args a, int R, int vec, int chunk_len) {
   extern __shared__ __align__(16) float smem[];
   const int KP = R * SCAN_KPT;                 // padded key size
   const int cols = SCAN_THREADS / R;           // value columns of this CTA
@@ -144,6 +144,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_arg
     const float* svs = sv + SCAN_TC * cols;
     const float* sb = svs + SCAN_TC;
 
+#pragma unroll 2
     for (int t = 0; t < nt; ++t) {
       const float4* q4 = reinterpret_cast<const float4*>(sq + t * KP);
       const float4* k4 = reinterpret_cast<const float4*>(sk + t * KP);
@@ -170,32 +171,44 @@ __global__ void __launch_bounds__(SCAN_THREADS) seq_scan_kernel(b2l_seq_scan_arg
       }
       const float vraw = sv[t * cols + cidx];
       float u = vraw * svs[t];
-      if (DELTA) {
-        float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
-#pragma unroll
-        for (int i = 0; i < SCAN_KPT; i += 4) {
-          p0 = fmaf(S[i], kr[i], p0); p1 = fmaf(S[i + 1], kr[i + 1], p1);
-          p2 = fmaf(S[i + 2], kr[i + 2], p2); p3 = fmaf(S[i + 3], kr[i + 3], p3);
-        }
-        float p = (p0 + p1) + (p2 + p3);
-        for (int o = 1; o < R; o <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
-        u = sb[t] * (u - p);
-      }
       if (PASS) {
 #pragma unroll
         for (int i = 0; i < SCAN_KPT; ++i) S[i] = fmaf(kr[i], u, S[i]);
         continue;
       }
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      float o;
+      if (DELTA) {
+        // With S' = diag(d) S:  u = beta (v - S'^T k)  and  o = (S' + k u^T)^T q = S'^T q + u (k.q): the three dot
+        // products over this lane's channels are reduced together, so a step has ONE shuffle chain on its critical path.
+        float p0 = 0.f, p1 = 0.f, o0 = 0.f, o1 = 0.f, c0 = 0.f, c1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < SCAN_KPT; i += 4) {
-        S[i] = fmaf(kr[i], u, S[i]); S[i + 1] = fmaf(kr[i + 1], u, S[i + 1]);
-        S[i + 2] = fmaf(kr[i + 2], u, S[i + 2]); S[i + 3] = fmaf(kr[i + 3], u, S[i + 3]);
-        o0 = fmaf(S[i], qr[i], o0); o1 = fmaf(S[i + 1], qr[i + 1], o1);
-        o2 = fmaf(S[i + 2], qr[i + 2], o2); o3 = fmaf(S[i + 3], qr[i + 3], o3);
+        for (int i = 0; i < SCAN_KPT; i += 2) {
+          p0 = fmaf(S[i], kr[i], p0); p1 = fmaf(S[i + 1], kr[i + 1], p1);
+          o0 = fmaf(S[i], qr[i], o0); o1 = fmaf(S[i + 1], qr[i + 1], o1);
+          c0 = fmaf(kr[i], qr[i], c0); c1 = fmaf(kr[i + 1], qr[i + 1], c1);
+        }
+        float p = p0 + p1, oq = o0 + o1, kq = c0 + c1;
+        for (int w = 1; w < R; w <<= 1) {
+          p += __shfl_xor_sync(0xffffffffu, p, w);
+          oq += __shfl_xor_sync(0xffffffffu, oq, w);
+          kq += __shfl_xor_sync(0xffffffffu, kq, w);
+        }
+        u = sb[t] * (u - p);
+#pragma unroll
+        for (int i = 0; i < SCAN_KPT; ++i) S[i] = fmaf(kr[i], u, S[i]);
+        o = fmaf(u, kq, oq);
+      } else {
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < SCAN_KPT; i += 4) {
+          S[i] = fmaf(kr[i], u, S[i]); S[i + 1] = fmaf(kr[i + 1], u, S[i + 1]);
+          S[i + 2] = fmaf(kr[i + 2], u, S[i + 2]); S[i + 3] = fmaf(kr[i + 3], u, S[i + 3]);
+          o0 = fmaf(S[i], qr[i], o0); o1 = fmaf(S[i + 1], qr[i + 1], o1);
+          o2 = fmaf(S[i + 2], qr[i + 2], o2); o3 = fmaf(S[i + 3], qr[i + 3], o3);
+        }
+        o = (o0 + o1) + (o2 + o3);
+        for (int w = 1; w < R; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
       }
-      float o = (o0 + o1) + (o2 + o3);
-      for (int w = 1; w < R; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
       if (r == 0) so[t * cols + cidx] = o * a.q_mult + skip * vraw;
     }
     __syncthreads();

@@ -149,10 +149,41 @@ def main(
     print(f"Memory used: {torch.cuda.max_memory_reserved() / 1e9:.02f} GB", file=sys.stderr)
 
 
+def main_model_dir(model_dir: str, prompt_ids: str, *, num_samples: int = 1, max_new_tokens: int = 50, top_k: Optional[int] = 200,
+                   temperature: float = 0.8, dtype: str = "bfloat16") -> None:
+    """Generation for any registered family from a folder with config.json + weights (registry.load_model), through the
+    engine's scheduler.  Prompts are token ids ("3,17,40"): a folder of this kind carries no tokenizer."""
+    from .engine import Engine
+    from .registry import load_model
+
+    device = torch.device("cuda", 0)
+    t0 = time.time()
+    model = load_model(model_dir, dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32, device=device,
+                       max_positions=len(prompt_ids.split(",")) + max_new_tokens)
+    print(f"Time to load model: {time.time() - t0:.02f} seconds.", file=sys.stderr)
+    engine = Engine(model, n_slots=max(1, num_samples))
+    prompt = [int(t) for t in prompt_ids.split(",") if t.strip()]
+    torch.manual_seed(1234)
+    for i in range(num_samples):
+        engine.add_request(i, prompt, max_new_tokens, temperature=temperature, top_k=top_k)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    out = engine.run()
+    torch.cuda.synchronize()
+    t = time.perf_counter() - t0
+    for i in range(num_samples):
+        print(",".join(str(x) for x in prompt + out[i]))
+    n = sum(len(v) for v in out.values())
+    print(f"Time for inference: {t:.02f} sec total, {n / t:.02f} tokens/sec", file=sys.stderr)
+
+
 def cli() -> None:
     import argparse
 
     ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("--model_dir", default=None, help="a folder with config.json + weights of any registered family (instead of --checkpoint_path)")
+    ap.add_argument("--prompt_ids", default="1", help="with --model_dir: the prompt as comma-separated token ids")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="with --model_dir")
     ap.add_argument("--prompt", default="Hello, my name is")
     ap.add_argument("--num_samples", type=int, default=1)
     ap.add_argument("--max_new_tokens", type=int, default=50)
@@ -162,7 +193,12 @@ def cli() -> None:
     ap.add_argument("--tokenizer_path", type=Path, default=Path("checkpoints/lit-llama/tokenizer.model"))
     ap.add_argument("--quantize", default=None, choices=[None, "llm.int8", "gptq.int4", "gptq.int8"])
     a = ap.parse_args()
-    main(**vars(a))
+    if a.model_dir is not None:
+        main_model_dir(a.model_dir, a.prompt_ids, num_samples=a.num_samples, max_new_tokens=a.max_new_tokens, top_k=a.top_k,
+                       temperature=a.temperature, dtype=a.dtype)
+        return
+    kw = {k: v for k, v in vars(a).items() if k not in ("model_dir", "prompt_ids", "dtype")}
+    main(**kw)
 
 
 if __name__ == "__main__":
