@@ -28,11 +28,15 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // Stage layout: q[TC][KP] k[TC][KP] d[TC][DP] v[TC][cols] vs[TC] beta[TC] (+ 2*TC unused: stages stay 16-byte aligned).
 // PASS 0: the recurrence with outputs, from the slot's state (one chunk) or from a chunk's start state in the workspace.
 // PASS 1: a chunk's local end state from zero and its total decay, no outputs (first pass of a chunked portion).
-template <int DELTA, typename act_t, int PASS>
-__global__ void __launch_bounds__(SCAN_THREADS, 2) seq_scan_kernel(b2l_seq_scan_args a, int R, int vec, int chunk_len) {
+// CPL: value columns per lane.  A step reads k, q and d from shared memory once per lane, so with one column the loop is
+// bound by shared-memory bandwidth (12 16-byte reads for 48 FMAs); two columns halve that where throughput matters (long
+// portions without the delta rule); one column keeps the most CTAs for single tokens and the latency-bound delta rule.
+template <int DELTA, typename act_t, int PASS, int CPL>
+__global__ void __launch_bounds__(SCAN_THREADS, DELTA ? 2 : 3) seq_scan_kernel(b2l_seq_scan_args a, int R, int vec, int chunk_len) {
   extern __shared__ __align__(16) float smem[];
   const int KP = R * SCAN_KPT;                 // padded key size
-  const int cols = SCAN_THREADS / R;           // value columns of this CTA
+  const int ncg = SCAN_THREADS / R;            // column groups: lane cidx holds columns cidx + j * ncg
+  const int cols = ncg * CPL;                  // value columns of this CTA
   const int DP = a.decay_per_channel ? KP : 4;
   const int stage = SCAN_TC * (2 * KP + DP + cols + 4);
   const int beta_at = SCAN_TC * (2 * KP + DP + cols + 1);
@@ -40,7 +44,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) seq_scan_kernel(b2l_seq_scan_
 
   const int tid = threadIdx.x, r = tid % R, cidx = tid / R;
   const int h = blockIdx.y, hq = h / (a.heads / a.qk_heads);
-  const int v0 = blockIdx.x * cols, vcol = v0 + cidx;
+  const int v0 = blockIdx.x * cols;
   const int K = a.K, V = a.V;
   const int slot = a.meta[0];
   const bool chunked = a.n_chunks > 1;
@@ -110,11 +114,15 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) seq_scan_kernel(b2l_seq_scan_
     return (DELTA && tid < min(SCAN_TC, t_end - t0)) ? ld_act((const act_t*)a.beta, (size_t)(t0 + tid) * a.ldb + h) : 0.f;
   };
 
-  float S[SCAN_KPT];
+  float S[CPL][SCAN_KPT];
 #pragma unroll
-  for (int i = 0; i < SCAN_KPT; ++i) {
-    const int kk = ((i >> 2) * R + r) * 4 + (i & 3);
-    S[i] = (PASS == 0 && kk < K && vcol < V) ? st[(size_t)vcol * K + kk] : 0.f;
+  for (int j = 0; j < CPL; ++j) {
+    const int vcol = v0 + cidx + j * ncg;
+#pragma unroll
+    for (int i = 0; i < SCAN_KPT; ++i) {
+      const int kk = ((i >> 2) * R + r) * 4 + (i & 3);
+      S[j][i] = (PASS == 0 && kk < K && vcol < V) ? st[(size_t)vcol * K + kk] : 0.f;
+    }
   }
   float P[PASS ? SCAN_KPT : 1];       // PASS 1: the chunk's total decay of this lane's key channels
 #pragma unroll
@@ -144,7 +152,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) seq_scan_kernel(b2l_seq_scan_
     const float* svs = sv + SCAN_TC * cols;
     const float* sb = svs + SCAN_TC;
 
-#pragma unroll 2
+#pragma unroll(DELTA ? 2 : 1)
     for (int t = 0; t < nt; ++t) {
       const float4* q4 = reinterpret_cast<const float4*>(sq + t * KP);
       const float4* k4 = reinterpret_cast<const float4*>(sk + t * KP);
@@ -160,56 +168,91 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) seq_scan_kernel(b2l_seq_scan_
 #pragma unroll
         for (int i4 = 0; i4 < SCAN_KPT / 4; ++i4) {
           const float4 dv = d4[i4 * R + r];
-          S[i4 * 4 + 0] *= dv.x; S[i4 * 4 + 1] *= dv.y; S[i4 * 4 + 2] *= dv.z; S[i4 * 4 + 3] *= dv.w;
+#pragma unroll
+          for (int j = 0; j < CPL; ++j) {
+            S[j][i4 * 4 + 0] *= dv.x; S[j][i4 * 4 + 1] *= dv.y; S[j][i4 * 4 + 2] *= dv.z; S[j][i4 * 4 + 3] *= dv.w;
+          }
           if (PASS) { P[i4 * 4 + 0] *= dv.x; P[i4 * 4 + 1] *= dv.y; P[i4 * 4 + 2] *= dv.z; P[i4 * 4 + 3] *= dv.w; }
         }
       } else {
         const float d = sd[t];
 #pragma unroll
-        for (int i = 0; i < SCAN_KPT; ++i) S[i] *= d;
+        for (int j = 0; j < CPL; ++j)
+#pragma unroll
+          for (int i = 0; i < SCAN_KPT; ++i) S[j][i] *= d;
         if (PASS) P[0] *= d;
       }
-      const float vraw = sv[t * cols + cidx];
-      float u = vraw * svs[t];
+      float vraw[CPL], u[CPL], o[CPL];
+#pragma unroll
+      for (int j = 0; j < CPL; ++j) {
+        vraw[j] = sv[t * cols + cidx + j * ncg];
+        u[j] = vraw[j] * svs[t];
+      }
       if (PASS) {
 #pragma unroll
-        for (int i = 0; i < SCAN_KPT; ++i) S[i] = fmaf(kr[i], u, S[i]);
+        for (int j = 0; j < CPL; ++j)
+#pragma unroll
+          for (int i = 0; i < SCAN_KPT; ++i) S[j][i] = fmaf(kr[i], u[j], S[j][i]);
         continue;
       }
-      float o;
       if (DELTA) {
-        // With S' = diag(d) S:  u = beta (v - S'^T k)  and  o = (S' + k u^T)^T q = S'^T q + u (k.q): the three dot
-        // products over this lane's channels are reduced together, so a step has ONE shuffle chain on its critical path.
-        float p0 = 0.f, p1 = 0.f, o0 = 0.f, o1 = 0.f, c0 = 0.f, c1 = 0.f;
+        // With S' = diag(d) S:  u = beta (v - S'^T k)  and  o = (S' + k u^T)^T q = S'^T q + u (k.q): the dot products
+        // over this lane's channels are reduced together, so a step has ONE shuffle chain on its critical path.
+        float c0 = 0.f, c1 = 0.f;
 #pragma unroll
         for (int i = 0; i < SCAN_KPT; i += 2) {
-          p0 = fmaf(S[i], kr[i], p0); p1 = fmaf(S[i + 1], kr[i + 1], p1);
-          o0 = fmaf(S[i], qr[i], o0); o1 = fmaf(S[i + 1], qr[i + 1], o1);
-          c0 = fmaf(kr[i], qr[i], c0); c1 = fmaf(kr[i + 1], qr[i + 1], c1);
+          c0 = fmaf(kr[i], qr[i], c0);
+          c1 = fmaf(kr[i + 1], qr[i + 1], c1);
         }
-        float p = p0 + p1, oq = o0 + o1, kq = c0 + c1;
+        float kq = c0 + c1, p[CPL], oq[CPL];
+#pragma unroll
+        for (int j = 0; j < CPL; ++j) {
+          float p0 = 0.f, p1 = 0.f, o0 = 0.f, o1 = 0.f;
+#pragma unroll
+          for (int i = 0; i < SCAN_KPT; i += 2) {
+            p0 = fmaf(S[j][i], kr[i], p0); p1 = fmaf(S[j][i + 1], kr[i + 1], p1);
+            o0 = fmaf(S[j][i], qr[i], o0); o1 = fmaf(S[j][i + 1], qr[i + 1], o1);
+          }
+          p[j] = p0 + p1;
+          oq[j] = o0 + o1;
+        }
         for (int w = 1; w < R; w <<= 1) {
-          p += __shfl_xor_sync(0xffffffffu, p, w);
-          oq += __shfl_xor_sync(0xffffffffu, oq, w);
           kq += __shfl_xor_sync(0xffffffffu, kq, w);
-        }
-        u = sb[t] * (u - p);
 #pragma unroll
-        for (int i = 0; i < SCAN_KPT; ++i) S[i] = fmaf(kr[i], u, S[i]);
-        o = fmaf(u, kq, oq);
+          for (int j = 0; j < CPL; ++j) {
+            p[j] += __shfl_xor_sync(0xffffffffu, p[j], w);
+            oq[j] += __shfl_xor_sync(0xffffffffu, oq[j], w);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < CPL; ++j) {
+          u[j] = sb[t] * (u[j] - p[j]);
+#pragma unroll
+          for (int i = 0; i < SCAN_KPT; ++i) S[j][i] = fmaf(kr[i], u[j], S[j][i]);
+          o[j] = fmaf(u[j], kq, oq[j]);
+        }
       } else {
-        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < SCAN_KPT; i += 4) {
-          S[i] = fmaf(kr[i], u, S[i]); S[i + 1] = fmaf(kr[i + 1], u, S[i + 1]);
-          S[i + 2] = fmaf(kr[i + 2], u, S[i + 2]); S[i + 3] = fmaf(kr[i + 3], u, S[i + 3]);
-          o0 = fmaf(S[i], qr[i], o0); o1 = fmaf(S[i + 1], qr[i + 1], o1);
-          o2 = fmaf(S[i + 2], qr[i + 2], o2); o3 = fmaf(S[i + 3], qr[i + 3], o3);
+        for (int j = 0; j < CPL; ++j) {
+          float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+          for (int i = 0; i < SCAN_KPT; i += 4) {
+            S[j][i] = fmaf(kr[i], u[j], S[j][i]); S[j][i + 1] = fmaf(kr[i + 1], u[j], S[j][i + 1]);
+            S[j][i + 2] = fmaf(kr[i + 2], u[j], S[j][i + 2]); S[j][i + 3] = fmaf(kr[i + 3], u[j], S[j][i + 3]);
+            o0 = fmaf(S[j][i], qr[i], o0); o1 = fmaf(S[j][i + 1], qr[i + 1], o1);
+            o2 = fmaf(S[j][i + 2], qr[i + 2], o2); o3 = fmaf(S[j][i + 3], qr[i + 3], o3);
+          }
+          o[j] = (o0 + o1) + (o2 + o3);
         }
-        o = (o0 + o1) + (o2 + o3);
-        for (int w = 1; w < R; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+        for (int w = 1; w < R; w <<= 1) {
+#pragma unroll
+          for (int j = 0; j < CPL; ++j) o[j] += __shfl_xor_sync(0xffffffffu, o[j], w);
+        }
       }
-      if (r == 0) so[t * cols + cidx] = o * a.q_mult + skip * vraw;
+      if (r == 0) {
+#pragma unroll
+        for (int j = 0; j < CPL; ++j) so[t * cols + cidx + j * ncg] = o[j] * a.q_mult + skip * vraw[j];
+      }
     }
     __syncthreads();
     if (PASS == 0) {
@@ -223,9 +266,13 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2) seq_scan_kernel(b2l_seq_scan_
 
   if (PASS == 0 && chunked) return;   // chunk outputs: the slot's state is written by the combine kernel
 #pragma unroll
-  for (int i = 0; i < SCAN_KPT; ++i) {
-    const int kk = ((i >> 2) * R + r) * 4 + (i & 3);
-    if (kk < K && vcol < V) st[(size_t)vcol * K + kk] = S[i];
+  for (int j = 0; j < CPL; ++j) {
+    const int vcol = v0 + cidx + j * ncg;
+#pragma unroll
+    for (int i = 0; i < SCAN_KPT; ++i) {
+      const int kk = ((i >> 2) * R + r) * 4 + (i & 3);
+      if (kk < K && vcol < V) st[(size_t)vcol * K + kk] = S[j][i];
+    }
   }
   if (PASS && blockIdx.x == 0 && cidx == 0) {
     float* wd = a.work_decay + ((size_t)blockIdx.z * a.heads + h) * (a.decay_per_channel ? K : 1);
@@ -259,7 +306,7 @@ __global__ void seq_scan_combine_kernel(b2l_seq_scan_args a) {
   st[i] = s;
 }
 
-static DynSmemCache g_scan_smem[6];
+static DynSmemCache g_scan_smem[10];
 constexpr int SCAN_CHUNK = 128;      // tokens per chunk of a chunked portion (a multiple of SCAN_TC)
 
 }  // namespace b2l
@@ -285,35 +332,37 @@ extern "C" int b2l_seq_scan(const b2l_seq_scan_args* a, b2l_stream_t stream) {
   const int chunk_len = n_chunks > 1 ? SCAN_CHUNK : a->T;
   int R = 1;
   while (R * SCAN_KPT < a->K) R <<= 1;
-  const int KP = R * SCAN_KPT, cols = SCAN_THREADS / R;
+  // two columns per lane where the loop is bound by shared-memory reads: long portions without the delta rule
+  const int cpl = (!a->delta && a->T >= 64 && a->V >= 2 * (SCAN_THREADS / R)) ? 2 : 1;
+  const int KP = R * SCAN_KPT, cols = (SCAN_THREADS / R) * cpl;
   const size_t smem = sizeof(float) * (2 * (size_t)SCAN_TC * (2 * KP + (a->decay_per_channel ? KP : 4) + cols + 4) + (size_t)SCAN_TC * cols);
   auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
   const int vec = a->K % 4 == 0 && a->ldq % 4 == 0 && a->ldk % 4 == 0 && al16(a->q) && al16(a->k) &&
                   (!a->decay_per_channel || (a->ldd % 4 == 0 && al16(a->decay)));
   dim3 grid((unsigned)((a->V + cols - 1) / cols), (unsigned)a->heads, (unsigned)n_chunks);
   cudaStream_t s = (cudaStream_t)stream;
-#define B2L_SCAN_LAUNCH(D, T_, P_, slot_)                                                 \
-  do {                                                                                    \
-    int rc_ = ensure_dyn_smem(seq_scan_kernel<D, T_, P_>, smem, g_scan_smem[slot_]);      \
-    if (rc_) return rc_;                                                                  \
-    seq_scan_kernel<D, T_, P_><<<grid, SCAN_THREADS, smem, s>>>(*a, R, vec, chunk_len);   \
+#define B2L_SCAN_LAUNCH(D, T_, P_, C_, slot_)                                                 \
+  do {                                                                                        \
+    int rc_ = ensure_dyn_smem(seq_scan_kernel<D, T_, P_, C_>, smem, g_scan_smem[slot_]);      \
+    if (rc_) return rc_;                                                                      \
+    seq_scan_kernel<D, T_, P_, C_><<<grid, SCAN_THREADS, smem, s>>>(*a, R, vec, chunk_len);   \
   } while (0)
+  const bool bf = a->act_dtype == B2L_BF16;
+  if (!bf && a->act_dtype != B2L_F32) {
+    set_error("b2l_seq_scan: act_dtype %d unsupported", a->act_dtype);
+    return B2L_E_UNSUPPORTED;
+  }
   if (n_chunks > 1) {   // local end states, combine, then the outputs below start from the workspace
-    if (a->act_dtype == B2L_BF16) B2L_SCAN_LAUNCH(0, __nv_bfloat16, 1, 4);
-    else if (a->act_dtype == B2L_F32) B2L_SCAN_LAUNCH(0, float, 1, 5);
+    if (cpl == 2) { if (bf) B2L_SCAN_LAUNCH(0, __nv_bfloat16, 1, 2, 4); else B2L_SCAN_LAUNCH(0, float, 1, 2, 5); }
+    else { if (bf) B2L_SCAN_LAUNCH(0, __nv_bfloat16, 1, 1, 6); else B2L_SCAN_LAUNCH(0, float, 1, 1, 7); }
     B2L_LAUNCH_CHECK("seq_scan_kernel (local states)");
     const size_t n = (size_t)a->heads * a->V * a->K;
     seq_scan_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(*a);
     B2L_LAUNCH_CHECK("seq_scan_combine_kernel");
   }
-  if (a->act_dtype == B2L_BF16) {
-    if (a->delta) B2L_SCAN_LAUNCH(1, __nv_bfloat16, 0, 0); else B2L_SCAN_LAUNCH(0, __nv_bfloat16, 0, 1);
-  } else if (a->act_dtype == B2L_F32) {
-    if (a->delta) B2L_SCAN_LAUNCH(1, float, 0, 2); else B2L_SCAN_LAUNCH(0, float, 0, 3);
-  } else {
-    set_error("b2l_seq_scan: act_dtype %d unsupported", a->act_dtype);
-    return B2L_E_UNSUPPORTED;
-  }
+  if (a->delta) { if (bf) B2L_SCAN_LAUNCH(1, __nv_bfloat16, 0, 1, 0); else B2L_SCAN_LAUNCH(1, float, 0, 1, 1); }
+  else if (cpl == 2) { if (bf) B2L_SCAN_LAUNCH(0, __nv_bfloat16, 0, 2, 2); else B2L_SCAN_LAUNCH(0, float, 0, 2, 3); }
+  else { if (bf) B2L_SCAN_LAUNCH(0, __nv_bfloat16, 0, 1, 8); else B2L_SCAN_LAUNCH(0, float, 0, 1, 9); }
 #undef B2L_SCAN_LAUNCH
   B2L_LAUNCH_CHECK("seq_scan_kernel");
   return 0;

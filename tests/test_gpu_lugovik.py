@@ -289,7 +289,7 @@ def test_delta_rule_scan_alone(K, V, H, G):
 
 @pytest.mark.parametrize("K,V,H,G,per_channel", [(24, 40, 2, 2, True), (8, 8, 1, 1, True), (24, 12, 4, 2, False), (64, 80, 2, 1, False)])
 def test_decayed_outer_product_scan_alone(K, V, H, G, per_channel):
-    T = 41
+    T = 77                             # above 64 tokens wide heads take the two-columns-per-lane form
     q, k, v = torch.randn(T, G, K), torch.randn(T, G, K) * 0.3, torch.randn(T, H, V)
     a = torch.rand(T, H, K) * 0.4 + 0.6 if per_channel else torch.rand(T, H) * 0.4 + 0.6
     dt, D = torch.rand(T, H) + 0.1, torch.randn(H)
