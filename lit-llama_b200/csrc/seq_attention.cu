@@ -166,17 +166,28 @@ __device__ __forceinline__ float4 ld4_act<__nv_bfloat16>(const __nv_bfloat16* p)
   return make_float4(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xffff0000u), __uint_as_float(w.y << 16), __uint_as_float(w.y & 0xffff0000u));
 }
 
+__device__ __forceinline__ void att_cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void att_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void att_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Key and value tiles stay in their storage type in shared memory (converted when read) and arrive by cp.async, one
+// tile ahead of the arithmetic: rows of K*sizeof + 16 bytes keep the 8 key rows of a ty group on distinct banks.
 template <typename act_t, int VC>
 __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(b2l_seq_attn_args a) {
   extern __shared__ __align__(16) float smem[];
-  const int K = a.K, V = 32 * VC, Kp = K + 4;
-  float* sQ = smem;                    // [TQ][Kp]
-  float* sK = sQ + TQ * Kp;            // [TK][Kp]
-  float* sV = sK + TK * Kp;            // [TK][V]
-  float* sP = sV + TK * V;             // [TQ][TK + 1]
+  constexpr int PER = 16 / (int)sizeof(act_t);            // elements per 16 bytes
+  const int K = a.K, V = 32 * VC, Kp = K + 4, Kpa = K + PER;
+  float* sQ = smem;                                       // [TQ][Kp] f32
+  float* sP = sQ + TQ * Kp;                               // [TQ][TK + 1]
+  act_t* sKb = reinterpret_cast<act_t*>(sP + TQ * (TK + 1) + 3);   // 2 x [TK][Kpa]
+  sKb = reinterpret_cast<act_t*>((reinterpret_cast<uintptr_t>(sKb)) & ~(uintptr_t)15);
+  act_t* sVb = sKb + 2 * TK * Kpa;                        // 2 x [TK][V]
   const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;
   const int h = blockIdx.y, g = h / (a.heads / a.kv_heads);
-  const int t_first = blockIdx.x * TQ, nq = min(TQ, a.T - t_first);
+  const int qt = gridDim.x - 1 - blockIdx.x;              // the longest tiles (last queries of a block) start first
+  const int t_first = qt * TQ, nq = min(TQ, a.T - t_first);
   const int slot = a.meta[0], pos0 = a.meta[1];
   const int p_first = pos0 + t_first, p_last = p_first + nq - 1;
   const int j_begin = (p_first / a.block) * a.block;
@@ -186,6 +197,32 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
   const act_t* ck = (const act_t*)a.cache_k + (size_t)slot * a.block * a.kv_heads * K;
   const act_t* cv = (const act_t*)a.cache_v + (size_t)slot * a.block * a.kv_heads * V;
 
+  auto issue_tile = [&](int jb, int buf) {
+    act_t* dK = sKb + buf * TK * Kpa;
+    act_t* dV = sVb + buf * TK * V;
+    const int kc = K / PER, vc = V / PER;                 // 16-byte pieces per row
+    for (int i = tid; i < TK * kc; i += TILE_THREADS) {
+      const int r = i / kc, c = (i - r * kc) * PER, j = jb + r;
+      if (j <= p_last) {
+        const int e = j % a.block;
+        att_cp_async16(dK + r * Kpa + c, j >= pos0 ? kn + ((size_t)(j - pos0) * a.kv_heads + g) * K + c : ck + ((size_t)e * a.kv_heads + g) * K + c);
+      } else {
+        *reinterpret_cast<uint4*>(dK + r * Kpa + c) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    for (int i = tid; i < TK * vc; i += TILE_THREADS) {
+      const int r = i / vc, c = (i - r * vc) * PER, j = jb + r;
+      if (j <= p_last) {
+        const int e = j % a.block;
+        att_cp_async16(dV + r * V + c, j >= pos0 ? vn + (size_t)(j - pos0) * a.ldv + (size_t)g * V + c : cv + ((size_t)e * a.kv_heads + g) * V + c);
+      } else {
+        *reinterpret_cast<uint4*>(dV + r * V + c) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    att_cp_commit();
+  };
+
+  issue_tile(j_begin, 0);
   const int K4 = K >> 2;
   for (int i = tid; i < TQ * K4; i += TILE_THREADS) {
     const int r = i / K4, c = (i - r * K4) << 2;
@@ -203,27 +240,17 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
     for (int c = 0; c < VC; ++c) acc[i][c][0] = acc[i][c][1] = acc[i][c][2] = acc[i][c][3] = 0.f;
   }
 
-  for (int jb = j_begin; jb <= p_last; jb += TK) {
-    __syncthreads();                   // the previous tile's K, V and P are no longer read (and sQ is written)
-    for (int i = tid; i < TK * K4; i += TILE_THREADS) {
-      const int r = i / K4, c = (i - r * K4) << 2, j = jb + r;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (j <= p_last) {
-        const int e = j % a.block;
-        v = ld4_act<act_t>(j >= pos0 ? kn + ((size_t)(j - pos0) * a.kv_heads + g) * K + c : ck + ((size_t)e * a.kv_heads + g) * K + c);
-      }
-      *reinterpret_cast<float4*>(sK + r * Kp + c) = v;
+  int buf = 0;
+  for (int jb = j_begin; jb <= p_last; jb += TK, buf ^= 1) {
+    if (jb + TK <= p_last) {
+      issue_tile(jb + TK, buf ^ 1);
+      att_cp_wait<1>();
+    } else {
+      att_cp_wait<0>();
     }
-    for (int i = tid; i < TK * (V >> 2); i += TILE_THREADS) {
-      const int r = i / (V >> 2), c = (i - r * (V >> 2)) << 2, j = jb + r;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (j <= p_last) {
-        const int e = j % a.block;
-        v = ld4_act<act_t>(j >= pos0 ? vn + (size_t)(j - pos0) * a.ldv + (size_t)g * V + c : cv + ((size_t)e * a.kv_heads + g) * V + c);
-      }
-      *reinterpret_cast<float4*>(sV + r * V + c) = v;
-    }
-    __syncthreads();
+    __syncthreads();                   // tile jb (and, the first time, sQ) is visible to every thread
+    const act_t* sK = sKb + buf * TK * Kpa;
+    const act_t* sV = sVb + buf * TK * V;
 
     float s[4][4];
 #pragma unroll
@@ -235,7 +262,7 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
 #pragma unroll
       for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4*>(sQ + (ty + 16 * i) * Kp + c);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) kv[j] = *reinterpret_cast<const float4*>(sK + (tx + 8 * j) * Kp + c);
+      for (int j = 0; j < 4; ++j) kv[j] = ld4_act<act_t>(sK + (tx + 8 * j) * Kpa + c);
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -290,7 +317,7 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
       for (int i = 0; i < 4; ++i) w[i] = sP[(ty + 16 * i) * (TK + 1) + j];
 #pragma unroll
       for (int c = 0; c < VC; ++c) {
-        const float4 v = *reinterpret_cast<const float4*>(sV + j * V + tx * 4 + 32 * c);
+        const float4 v = ld4_act<act_t>(sV + j * V + tx * 4 + 32 * c);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           acc[i][c][0] = fmaf(w[i], v.x, acc[i][c][0]); acc[i][c][1] = fmaf(w[i], v.y, acc[i][c][1]);
@@ -298,6 +325,7 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
         }
       }
     }
+    __syncthreads();                   // this tile's buffers and sP may be overwritten
   }
 
 #pragma unroll
@@ -317,11 +345,17 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
   }
 }
 
+template <typename act_t>
+static size_t tile_smem_bytes(int K, int V) {
+  const int per = 16 / (int)sizeof(act_t);
+  return sizeof(float) * ((size_t)TQ * (K + 4) + (size_t)TQ * (TK + 1) + 4) + sizeof(act_t) * 2 * ((size_t)TK * (K + per) + (size_t)TK * V) + 16;
+}
+
 static DynSmemCache g_tile_smem[8];
 
 template <typename act_t, int VC>
 static int launch_tile(const b2l_seq_attn_args* a, cudaStream_t s, int cache_slot) {
-  const size_t smem = sizeof(float) * ((size_t)(TQ + TK) * (a->K + 4) + (size_t)TK * 32 * VC + (size_t)TQ * (TK + 1));
+  const size_t smem = tile_smem_bytes<act_t>(a->K, 32 * VC);
   int rc = ensure_dyn_smem(seq_block_attention_tile_kernel<act_t, VC>, smem, g_tile_smem[cache_slot]);
   if (rc) return rc;
   dim3 grid((unsigned)((a->T + TQ - 1) / TQ), (unsigned)a->heads);
@@ -368,8 +402,9 @@ extern "C" int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t 
   const size_t smem = sizeof(float) * ((size_t)(split ? 1 : 4) * Kpad + (split ? 16 : 4) * (2 + ATT_VMAX * 32));
   B2L_CHECK_SUPPORTED(smem <= 48 * 1024, "b2l_seq_block_attention: key size %d too large", a->K);
   const bool al = (((uintptr_t)a->q | (uintptr_t)a->k_new | (uintptr_t)a->v_new | (uintptr_t)a->cache_k | (uintptr_t)a->cache_v) % 16) == 0;
-  const size_t tile_smem = sizeof(float) * ((size_t)(TQ + TK) * (a->K + 4) + (size_t)TK * a->V + (size_t)TQ * (TK + 1));
-  const bool tile = !split && a->T >= 16 && al && a->K % 4 == 0 && a->V % 32 == 0 && a->V <= 128 && a->ldv % 4 == 0 && tile_smem <= 200 * 1024;
+  const size_t tile_smem = a->act_dtype == B2L_BF16 ? tile_smem_bytes<__nv_bfloat16>(a->K, a->V) : tile_smem_bytes<float>(a->K, a->V);
+  const bool tile = !split && a->T >= 16 && al && (a->K * esz) % 16 == 0 && a->V % 32 == 0 && a->V <= 128 && (a->ldv * esz) % 16 == 0 &&
+                    tile_smem <= 200 * 1024;
   if (tile) {
     const int vc = a->V / 32;
     int rc = 0;

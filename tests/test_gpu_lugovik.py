@@ -474,6 +474,18 @@ def test_grouped_read_out_norm_small_and_large_groups(group, n):
     assert rel(res, ref) < 1e-6
 
 
+@pytest.mark.parametrize("F,dtype", [(33, torch.float32), (64, torch.float32), (4096, torch.bfloat16), (40, torch.bfloat16), (36, torch.bfloat16)])
+def test_gated_activation_both_forms(F, dtype):
+    _, S, M = _pkg()
+    T = 5
+    ctx = _ctx(T, dtype=dtype)
+    gu = (torch.randn(T, 2 * F) * 3).to(dtype)
+    mid = torch.empty(T, F, device=DEV, dtype=dtype)
+    for act, fn in ((S.ACT_GELU_TANH, O.gelu_tanh), (S.ACT_SILU, O.silu)):
+        S.check(S.lib().b2l_seq_gated_act(M._p(dev(gu)), 2 * F, M._p(mid), T, F, act, ctx.act, ctx.stream), "act")
+        assert rel(mid, fn(gu[:, :F].double()) * gu[:, F:].double()) < (1e-6 if dtype == torch.float32 else 4e-3)
+
+
 def test_row_kernels():
     """Embedding scale, RMS norm with row selection, post-norm + residual + next pre-norm, gated activation, grouped
     read-out norm with its gate in both orders, both decay forms (including arguments where exp or sigmoid saturate)."""
