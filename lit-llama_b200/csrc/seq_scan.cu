@@ -297,11 +297,21 @@ __global__ void seq_scan_combine_kernel(b2l_seq_scan_args a) {
   const int h = (int)(i / per_head), kk = (int)(i % a.K);
   float* st = a.state + (size_t)a.meta[0] * n;
   float s = st[i];
-  for (int c = 0; c < a.n_chunks; ++c) {
-    const float d = a.work_decay[((size_t)c * a.heads + h) * (a.decay_per_channel ? a.K : 1) + (a.decay_per_channel ? kk : 0)];
-    const float local = a.work_state[(size_t)c * n + i];
-    a.work_state[(size_t)c * n + i] = s;
-    s = fmaf(d, s, local);
+  const size_t dstep = (size_t)a.heads * (a.decay_per_channel ? a.K : 1);
+  const float* dp = a.work_decay + (size_t)h * (a.decay_per_channel ? a.K : 1) + (a.decay_per_channel ? kk : 0);
+  for (int c0 = 0; c0 < a.n_chunks; c0 += 8) {        // eight chunks' operands are requested together
+    float d[8], local[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const bool in = c0 + u < a.n_chunks;
+      d[u] = in ? dp[(size_t)(c0 + u) * dstep] : 1.f;
+      local[u] = in ? a.work_state[(size_t)(c0 + u) * n + i] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (c0 + u < a.n_chunks) a.work_state[(size_t)(c0 + u) * n + i] = s;
+      s = fmaf(d[u], s, local[u]);
+    }
   }
   st[i] = s;
 }
