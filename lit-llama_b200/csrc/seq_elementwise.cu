@@ -420,16 +420,16 @@ extern "C" int b2l_seq_gated_act(const void* gu, int ldgu, void* out, int T, int
 
 extern "C" int b2l_seq_conv_silu(const void* in, int ldin, const void* w, const void* bias, void* state, const int* meta,
                                  float* out, int ldout, int T, int C, int taps, int act_dtype, b2l_stream_t stream) {
-  B2L_CHECK_ARG(in && w && state && meta && out, "b2l_seq_conv_silu: null pointer");
+  B2L_CHECK_ARG(in && w && (state || taps == 1) && meta && out, "b2l_seq_conv_silu: null pointer");
   B2L_CHECK_ARG(T >= 0 && C > 0 && ldin >= C && ldout >= C, "b2l_seq_conv_silu: bad size");
-  B2L_CHECK_SUPPORTED(taps >= 2 && taps <= CONV_MAX_TAPS, "b2l_seq_conv_silu: taps %d outside 2..%d", taps, CONV_MAX_TAPS);
+  B2L_CHECK_SUPPORTED(taps >= 1 && taps <= CONV_MAX_TAPS, "b2l_seq_conv_silu: taps %d outside 1..%d", taps, CONV_MAX_TAPS);
   if (T == 0) return 0;
   const int tiles = (T + CONV_TT - 1) / CONV_TT;
   dim3 grid((unsigned)((C + 127) / 128), (unsigned)tiles);
   B2L_SEQ_DISPATCH(act_dtype, {
     seq_conv_silu_kernel<act_t><<<grid, 128, 0, (cudaStream_t)stream>>>((const act_t*)in, ldin, (const act_t*)w, (const act_t*)bias,
                                                                         (act_t*)state, meta, out, ldout, T, C, taps, tiles == 1);
-    if (tiles > 1)   // T > CONV_TT >= taps - 1: the new state comes from the portion alone
+    if (tiles > 1 && taps > 1)   // T > CONV_TT >= taps - 1: the new state comes from the portion alone
       seq_conv_state_kernel<act_t><<<(C + 127) / 128, 128, 0, (cudaStream_t)stream>>>((const act_t*)in, ldin, (act_t*)state, meta, T, C, taps);
   });
   B2L_LAUNCH_CHECK("seq_conv_silu_kernel");
