@@ -62,7 +62,19 @@ def cfg_b():
     ]}
 
 
-CONFIGS = {"a": cfg_a, "b": cfg_b}
+def cfg_c():
+    """Shapes that take the tiled attention kernel, the chunk-parallel scans and two value columns per lane."""
+    return {"architecture": "Lugovik", "vocab": 200, "width": 160, "norm": {"eps": 1e-6}, "embedding": {"scale": 12.0}, "layers": [
+        {"type": "mamba2", "mlp": {"kind": "dense", "ff": 192}, "mixer": {"conv": 4, "groups": 1, "heads": 3, "norm_groups": 3, "state": 40, "vdim": 64}},
+        {"type": "parallel", "mlp": {"kind": "dense", "ff": 192}, "mixer": {
+            "left": {"heads": 4, "kv_heads": 1, "dim": 40, "vdim": 64, "mask": {"size": 100}, "scale": 0.16, "softcap": 30.0,
+                     "rot": {"base": 5000.0, "dims": 32, "scaling": {"factor": 4.0, "original": 128, "fast": 16.0, "slow": 2.0}}},
+            "right": {"heads": 2, "dim": 16, "vdim": 48, "tau": 8.0, "rank": 4}, "left_scale": 1.5, "right_scale": 0.5}},
+        {"type": "channel_delta", "mlp": {"kind": "dense", "ff": 192}, "mixer": {"conv": 3, "dim": 48, "heads": 2, "kv_heads": 1, "vdim": 64, "rank": 12}},
+    ]}
+
+
+CONFIGS = {"a": cfg_a, "b": cfg_b, "c": cfg_c}
 
 
 def build(cfg, dtype, seed=1, n_slots=3, **kw):
@@ -186,6 +198,19 @@ def test_a_long_prompt_in_one_portion_and_in_pieces():
     parts = run_schedule(engine, "p", toks, cuts_of(600, [100, 3, 270, 1]))
     assert rel(whole, parts) < 2e-5
     assert max(rel(whole[t], want[t]) for t in range(0, 600, 7)) < 4 * F32_TOL
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, F32_TOL), (torch.bfloat16, BF16_TOL)])
+def test_long_prompt_on_the_prompt_kernels(dtype, tol):
+    """500 tokens of a model whose shapes select the tiled attention kernel and the chunk-parallel scans, whole and cut
+    inside blocks and chunks, then decoded tokens, against the plain model."""
+    cfg = cfg_c()
+    engine, W = build(cfg, dtype)
+    toks = tokens_for(cfg, 520, seed=6)
+    want = O.forward(cfg, W, toks)
+    for cuts in ([500] + [1] * 20, [130, 270, 3, 97] + [1] * 20):
+        got = run_schedule(engine, "r", toks, cuts)
+        assert max(rel(got[t], want[t]) for t in list(range(0, 520, 9)) + list(range(495, 520))) < 4 * tol, cuts[:4]
 
 
 def test_long_decoding_across_many_blocks():
