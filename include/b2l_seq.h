@@ -132,6 +132,86 @@ int b2l_seq_cast_f32(const void* in, int ldin, float* out, int ldout, int T, int
 /* Zero one slot of a state tensor laid out [n_slots][slot_bytes]. */
 int b2l_seq_zero_slot(void* state, size_t slot_bytes, int slot, b2l_stream_t stream);
 
+/* ---- two sublayers on the same input ----
+ * x[r] += y1[r] + y2[r] (act, either may be null; the sum is f32), then up to two RMS norms of the new row with weights
+ * stored around w_offset: h[r] = x[r] / sqrt(mean(x[r]^2) + eps) * (w_offset + w).  w2 / h2 may be null, and so may
+ * w1 / h1 (then only the sum is done).  `rows` (device int32[n_rows], may be null, only when y1 is null) picks the
+ * rows of x that are normalised (out row r <- x row rows[r]). */
+int b2l_seq_add_norm2(const void* y1, const void* y2, float* x, const void* w1, void* h1, const void* w2, void* h2,
+                      float w_offset, float eps, const int* rows, int n_rows, int D, int act_dtype, b2l_stream_t stream);
+
+/* z <- cap * tanh(z / cap) in place on f32 (soft cap of logits). */
+int b2l_seq_softcap(float* z, size_t n, float cap, b2l_stream_t stream);
+
+/* Partial rotation by position, any layout.  Per head (`size` entries, heads every hsx elements of x and hso of out):
+ * the entries [rot_off, rot_off + rot_dims) are rotated by the angle (pos0 + t) * freq[i]: pair (2i, 2i+1) when
+ * interleaved, else (i, i + rot_dims/2); (u, v) -> (u cos - v sin, v cos + u sin).  Every entry is multiplied by
+ * `mult` afterwards.  x is f32 (in_f32) or act, out f32 (out_f32) or act. */
+int b2l_seq_rope(const void* x, int ldx, int in_f32, const float* freq, int rot_dims, int interleaved, int rot_off, float mult,
+                 const int* meta, void* out, int ldo, int out_f32, int T, int heads, int size, int hsx, int hso, int act_dtype,
+                 b2l_stream_t stream);
+
+/* ---- latent attention ----
+ * Keys and values of all heads are linear images of one latent vector per position; beside it one rotated key part
+ * is shared by all heads.  The cache holds [latent (rank) | rotated key (rot_dim)] per position:
+ * [n_slots][max_pos][rank + rot_dim] act.
+ *
+ * b2l_seq_latent_prep, on the f32 product proj [T, ld] of the two down-projections:
+ *   cq[t]  = rmsnorm(proj[t, q_off : q_off + q_rank]) * w_q                    (act [T, q_rank])
+ *   cache[slot][pos0 + t] = [ rmsnorm(proj[t, kv_off : kv_off + rank]) * w_kv | rotate(proj[t, kv_off + rank : .. + rot_dim]) ]
+ * with the rotation of b2l_seq_rope on the first rot_dims entries of the rotated part. */
+int b2l_seq_latent_prep(const float* proj, int ld, int q_off, int q_rank, const void* w_q, void* cq, int kv_off, int rank,
+                        const void* w_kv, int rot_dim, const float* freq, int rot_dims, int interleaved, float eps,
+                        const int* meta, void* cache, int max_pos, int T, int act_dtype, b2l_stream_t stream);
+
+/* Causal softmax attention of T x heads query rows over the cached positions 0 .. pos0 + t, in the latent space:
+ *   score = (q_lat . latent_j + q_rot . rotated_key_j) * scale;  weights exp(score_j) / (exp(sink[h]) + sum_j exp(score_j))
+ *   out[t, h*rank : (h+1)*rank] = sum_j weight_j latent_j
+ * q_lat is the query already multiplied by the key up-projection (f32, element [t][h][d] at t*ldq_t + h*ldq_h + d),
+ * q_rot the rotated query part (f32, row (t, h) at (t*heads + h)*ldr + rot_off).  The cache must already hold the
+ * portion's own positions (b2l_seq_latent_prep).  `splits` > 1 cuts the keys into that many ranges that run in
+ * parallel and are merged afterwards; it needs work: f32 [splits][T*heads][rank + 2].  The grid does not depend on
+ * the position, so a captured single-token step replays anywhere. */
+typedef struct {
+  const float* q_lat; long long ldq_t; long long ldq_h;
+  const float* q_rot; int ldr; int rot_off;
+  const void* cache; int max_pos;
+  const float* sink;               /* f32 [heads] */
+  const int* meta;
+  void* out; int ldo;              /* act [T, ldo] */
+  float* work;
+  float scale;
+  int T, heads, rank, rot_dim, splits, act_dtype;
+} b2l_seq_latent_attn_args;
+int b2l_seq_latent_attention(const b2l_seq_latent_attn_args* a, b2l_stream_t stream);
+int b2l_seq_latent_attention_warps(int T, int heads);    /* warps per CTA the call will use: 4 rows per warp */
+
+/* ---- mixture of experts ----
+ * Router, per token, from f32 logits [T, ld] over n experts: s = softmax(logits); choice = s + correction (f32 [n],
+ * may be null); the n experts form `groups` equal groups of neighbours, a group's score is its largest choice score,
+ * only experts of the `keep` best groups can be chosen; idx[t, :] = the `top` largest choice scores among them (best
+ * first), weights[t, k] = s[idx] / (sum of the chosen s + 1e-20). */
+int b2l_seq_moe_route(const float* logits, int ld, const float* correction, int n, int groups, int keep, int top, int* idx,
+                      float* weights, int T, b2l_stream_t stream);
+
+/* Experts of a few tokens, indices read on the device.  Expert e < n_real: W_down[e] (silu(W_gate[e] h) * (W_up[e] h))
+ * with w_gate_up act [n_real][2*ff][D] (gate rows, then up rows) and w_down act [n_real][D][ff]; e >= n_real: h itself.
+ * y[t] = sum_k weights[t, k] * expert_idx[t,k](h[t]).  mid: act [T*top, ff] scratch. */
+int b2l_seq_moe_experts_small(const void* h, int ldh, const void* w_gate_up, const void* w_down, const int* idx,
+                              const float* weights, void* mid, void* y, int ldy, int T, int D, int ff, int n_real, int top,
+                              int act_dtype, b2l_stream_t stream);
+
+/* Long portions: the N = T*top assignments a = t*top + k sorted by expert.  offsets int32[n_real + 1]: expert e owns
+ * the sorted places offsets[e] .. offsets[e+1]-1; perm[p] = assignment at place p; inv[a] = place of assignment a
+ * (-1: an identity expert).  cursor: int32[n_real + 1] scratch. */
+int b2l_seq_moe_sort(const int* idx, int N, int n_real, int* offsets, int* cursor, int* perm, int* inv, b2l_stream_t stream);
+/* xg[p, :] = h[perm[p] / top, :] for p < *n_rows (device int32: offsets[n_real]); launched over N rows. */
+int b2l_seq_moe_gather(const void* h, int ldh, const int* perm, const int* n_rows, int top, void* xg, int N, int D,
+                       int act_dtype, b2l_stream_t stream);
+/* y[t] = sum_k weights[t, k] * (inv[a] >= 0 ? yg[inv[a]] : h[t]). */
+int b2l_seq_moe_combine(const void* yg, const int* inv, const float* weights, const void* h, int ldh, void* y, int ldy, int T,
+                        int D, int top, int act_dtype, b2l_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -46,6 +46,20 @@ class AttnArgs(C.Structure):
     ]
 
 
+class LatentAttnArgs(C.Structure):
+    _fields_ = [
+        ("q_lat", c_void_p), ("ldq_t", C.c_longlong), ("ldq_h", C.c_longlong),
+        ("q_rot", c_void_p), ("ldr", c_int), ("rot_off", c_int),
+        ("cache", c_void_p), ("max_pos", c_int),
+        ("sink", c_void_p),
+        ("meta", c_void_p),
+        ("out", c_void_p), ("ldo", c_int),
+        ("work", c_void_p),
+        ("scale", c_float),
+        ("T", c_int), ("heads", c_int), ("rank", c_int), ("rot_dim", c_int), ("splits", c_int), ("act_dtype", c_int),
+    ]
+
+
 _SIGS = {
     "b2l_seq_version": (c_int, []),
     "b2l_seq_last_error": (C.c_char_p, []),
@@ -67,6 +81,21 @@ _SIGS = {
     "b2l_seq_block_attention": (c_int, [C.POINTER(AttnArgs), c_void_p]),
     "b2l_seq_cast_f32": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "b2l_seq_zero_slot": (c_int, [c_void_p, c_size_t, c_int, c_void_p]),
+    "b2l_seq_add_norm2": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_int,
+                                  c_int, c_int, c_void_p]),
+    "b2l_seq_softcap": (c_int, [c_void_p, c_size_t, c_float, c_void_p]),
+    "b2l_seq_rope": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                             c_int, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_latent_prep": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+                                    c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_latent_attention": (c_int, [C.POINTER(LatentAttnArgs), c_void_p]),
+    "b2l_seq_latent_attention_warps": (c_int, [c_int, c_int]),
+    "b2l_seq_moe_route": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "b2l_seq_moe_experts_small": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                          c_int, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_moe_sort": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b2l_seq_moe_gather": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
 }
 
 EXPORTS = tuple(_SIGS)

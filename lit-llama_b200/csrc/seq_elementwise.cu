@@ -510,3 +510,69 @@ extern "C" int b2l_seq_headnorm_rope(const void* x, int ldx, const void* w, floa
   B2L_LAUNCH_CHECK("seq_headnorm_rope_kernel");
   return 0;
 }
+
+// ---- residual streams with two sublayers on the same input ----
+namespace b2l {
+
+// x += y1 + y2 (each may be null), then up to two RMS norms of the new row with weights stored around `w_offset`
+// (h = x / rms(x) * (w_offset + w)): a layer whose mixer and feed-forward read the same x with a norm each.  `rows`
+// picks the rows (out row r <- x row rows[r]) when nothing is added.  One CTA per row; the sum is f32.
+template <typename act_t>
+__global__ void __launch_bounds__(256) seq_add_norm2_kernel(const act_t* __restrict__ y1, const act_t* __restrict__ y2, float* __restrict__ x,
+                                                            const act_t* __restrict__ w1, act_t* __restrict__ h1,
+                                                            const act_t* __restrict__ w2, act_t* __restrict__ h2, float w_offset, float eps,
+                                                            const int* __restrict__ rows, int D) {
+  __shared__ float red[32];
+  const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+  float* xr = x + (size_t)r * D;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float v = xr[i];
+    if (y1) {
+      float add = ld_act(y1, (size_t)r * D + i);
+      if (y2) add += ld_act(y2, (size_t)r * D + i);
+      v += add;
+      xr[i] = v;
+    }
+    ss += v * v;
+  }
+  if (w1 == nullptr) return;
+  ss = block_sum(ss, red);
+  const float rinv = 1.0f / sqrtf(ss / (float)D + eps);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {       // own writes of xr: visible to this thread
+    const float v = xr[i] * rinv;
+    st_act(h1, (size_t)blockIdx.x * D + i, v * (w_offset + ld_act(w1, i)));
+    if (w2) st_act(h2, (size_t)blockIdx.x * D + i, v * (w_offset + ld_act(w2, i)));
+  }
+}
+
+__global__ void seq_softcap_kernel(float* __restrict__ z, size_t n, float cap) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) z[i] = cap * tanhf(z[i] / cap);
+}
+
+}  // namespace b2l
+
+extern "C" int b2l_seq_add_norm2(const void* y1, const void* y2, float* x, const void* w1, void* h1, const void* w2, void* h2,
+                                 float w_offset, float eps, const int* rows, int n_rows, int D, int act_dtype, b2l_stream_t stream) {
+  B2L_CHECK_ARG(x != nullptr && (y1 != nullptr || y2 == nullptr), "b2l_seq_add_norm2: null pointer");
+  B2L_CHECK_ARG((w1 == nullptr) == (h1 == nullptr) && (w2 == nullptr) == (h2 == nullptr) && (w1 != nullptr || w2 == nullptr),
+                "b2l_seq_add_norm2: every norm needs its weight and its output, the second norm needs the first");
+  B2L_CHECK_ARG(rows == nullptr || y1 == nullptr, "b2l_seq_add_norm2: rows are picked only when nothing is added");
+  B2L_CHECK_ARG(n_rows >= 0 && D > 0, "b2l_seq_add_norm2: bad size");
+  if (n_rows == 0 || (y1 == nullptr && w1 == nullptr)) return 0;
+  B2L_SEQ_DISPATCH(act_dtype, {
+    seq_add_norm2_kernel<act_t><<<n_rows, 256, 0, (cudaStream_t)stream>>>((const act_t*)y1, (const act_t*)y2, x, (const act_t*)w1, (act_t*)h1,
+                                                                         (const act_t*)w2, (act_t*)h2, w_offset, eps, rows, D);
+  });
+  B2L_LAUNCH_CHECK("seq_add_norm2_kernel");
+  return 0;
+}
+
+extern "C" int b2l_seq_softcap(float* z, size_t n, float cap, b2l_stream_t stream) {
+  B2L_CHECK_ARG(z != nullptr && cap > 0.f, "b2l_seq_softcap: null pointer or cap <= 0");
+  if (n == 0) return 0;
+  const int grid = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  b2l::seq_softcap_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(z, n, cap);
+  B2L_LAUNCH_CHECK("seq_softcap_kernel");
+  return 0;
+}

@@ -1,0 +1,346 @@
+// Latent attention: keys and values of every head are linear images of one cached latent vector per position, plus
+// one rotated key part shared by all heads.  Only [latent | rotated key] is cached.  The attention runs in the
+// latent space ("absorbed" form): with q' = W_uk^T q_unrotated per head,
+//     score(i, j) = (q'_i . c_j + q_rot_i . k_rot_j) * scale,     o'_i = sum_j weight(i, j) c_j,
+// and the caller maps o' to the value space (W_uv) afterwards.  All heads of all queries are rows over the same
+// keys, so one key tile in shared memory serves every row of a CTA.  Softmax has one learned sink per head in the
+// denominator (exp(sink_h), no key, no value).  Scores, weights and accumulators are f32.
+#include "seq_common.cuh"
+
+namespace b2l {
+
+// A general partial rotation.  Per head of `size` entries: entries [off, off + rot_dims) are rotated by the angle
+// (pos0 + t) * freq[i], pairs (2i, 2i+1) when interleaved, else (i, i + rot_dims/2); everything is multiplied by
+// `mult` afterwards.  Heads start every hsx (input) / hso (output) elements.  One warp per (token, head).
+template <typename in_t, typename out_t>
+__global__ void seq_rope_kernel(const in_t* __restrict__ x, int ldx, const float* __restrict__ freq, int rot_dims, int interleaved,
+                                int off, float mult, const int* __restrict__ meta, out_t* __restrict__ out, int ldo, int n_rows, int heads,
+                                int size, int hsx, int hso) {
+  const int id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (id >= n_rows * heads) return;
+  const int t = id / heads, hd = id % heads;
+  const in_t* p = x + (size_t)t * ldx + (size_t)hd * hsx;
+  out_t* q = out + (size_t)t * ldo + (size_t)hd * hso;
+  const float pos = (float)(meta[1] + t);
+  const int half = rot_dims / 2;
+  for (int i = lane; i < off; i += 32) st_act(q, i, ld_act(p, i) * mult);
+  for (int i = lane; i < half; i += 32) {
+    const int iu = off + (interleaved ? 2 * i : i), iv = off + (interleaved ? 2 * i + 1 : i + half);
+    const float u = ld_act(p, iu), v = ld_act(p, iv);
+    float s, c;
+    sincosf(pos * freq[i], &s, &c);
+    st_act(q, iu, (u * c - v * s) * mult);
+    st_act(q, iv, (v * c + u * s) * mult);
+  }
+  for (int i = off + rot_dims + lane; i < size; i += 32) st_act(q, i, ld_act(p, i) * mult);
+}
+
+// One CTA per token of the portion, on the f32 product [W_dq ; W_dkv] h:
+//   cq  = rmsnorm(proj[q_off : q_off + q_rank]) * wq                       -> cq (act), input of the query up-projection
+//   c   = rmsnorm(proj[kv_off : kv_off + rank]) * wkv                      -> cache[slot][pos][0 : rank]
+//   k_r = rotate(proj[kv_off + rank : kv_off + rank + rot_dim])            -> cache[slot][pos][rank : rank + rot_dim]
+template <typename act_t>
+__global__ void __launch_bounds__(128) seq_latent_prep_kernel(const float* __restrict__ proj, int ld, int q_off, int q_rank,
+                                                              const act_t* __restrict__ wq, act_t* __restrict__ cq, int kv_off, int rank,
+                                                              const act_t* __restrict__ wkv, int rot_dim, const float* __restrict__ freq,
+                                                              int rot_dims, int interleaved, float eps, const int* __restrict__ meta,
+                                                              act_t* __restrict__ cache, int max_pos) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const float* row = proj + (size_t)t * ld;
+  {
+    const float* a = row + q_off;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) ss += a[i] * a[i];
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)q_rank + eps);
+    act_t* o = cq + (size_t)t * q_rank;
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) st_act(o, i, a[i] * r * ld_act(wq, i));
+  }
+  const int slot = meta[0], pos = meta[1] + t;
+  const float* a = row + kv_off;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) ss += a[i] * a[i];
+  ss = block_sum(ss, red);
+  if (pos < 0 || pos >= max_pos) return;      // the pool never hands out such a position
+  const float r = 1.0f / sqrtf(ss / (float)rank + eps);
+  act_t* dst = cache + ((size_t)slot * max_pos + pos) * (size_t)(rank + rot_dim);
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) st_act(dst, i, a[i] * r * ld_act(wkv, i));
+  const float* b = a + rank;
+  const int half = rot_dims / 2;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const int iu = interleaved ? 2 * i : i, iv = interleaved ? 2 * i + 1 : i + half;
+    float s, c;
+    sincosf((float)pos * freq[i], &s, &c);
+    st_act(dst, rank + iu, b[iu] * c - b[iv] * s);
+    st_act(dst, rank + iv, b[iv] * c + b[iu] * s);
+  }
+  for (int i = rot_dims + threadIdx.x; i < rot_dim; i += blockDim.x) st_act(dst, rank + i, b[i]);
+}
+
+constexpr int LAT_RW = 4;       // rows (query, head) per warp
+constexpr int LAT_BN = 32;      // keys per tile: one per lane
+constexpr int LAT_LDK = 33;     // padded key count of the transposed tile
+
+// Rows r = t * heads + h.  A warp owns LAT_RW consecutive rows, a CTA blockDim/32 warps; grid.y splits the keys.
+// Shared: kT[Kp][33] (the key tile transposed, f32), qs[rows][Kp], ps[rows][32].  Scores: lane j owns key j of the
+// tile (q read as broadcast float4, kT conflict-free).  Values: lane owns latent entries lane + 32 i (weights read
+// as broadcast float4, kT with stride 33 conflict-free).
+template <typename act_t, int VI>
+__global__ void __launch_bounds__(256) seq_latent_attention_kernel(b2l_seq_latent_attn_args a) {
+  extern __shared__ __align__(16) float lat_smem[];
+  const int Kd = a.rank + a.rot_dim, Kp = (Kd + 3) & ~3;
+  const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rows_cta = nw * LAT_RW, R = a.T * a.heads;
+  float* kT = lat_smem;
+  float* qs = kT + (size_t)Kp * LAT_LDK;
+  float* ps = qs + (size_t)rows_cta * Kp;
+  const int slot = a.meta[0], pos0 = a.meta[1];
+  const int row0 = blockIdx.x * rows_cta;
+  const act_t* cache = reinterpret_cast<const act_t*>(a.cache) + (size_t)slot * a.max_pos * Kd;
+
+  // queries of this CTA's rows -> shared (zero beyond the row count and in the padding)
+  for (int i = threadIdx.x; i < rows_cta * Kp; i += blockDim.x) {
+    const int rl = i / Kp, d = i % Kp, r = row0 + rl;
+    float v = 0.f;
+    if (r < R && d < Kd) {
+      const int t = r / a.heads, h = r % a.heads;
+      v = d < a.rank ? a.q_lat[(size_t)t * a.ldq_t + (size_t)h * a.ldq_h + d] : a.q_rot[((size_t)t * a.heads + h) * a.ldr + a.rot_off + (d - a.rank)];
+    }
+    qs[i] = v;
+  }
+  for (int i = threadIdx.x; i < (Kp - Kd) * LAT_LDK; i += blockDim.x) kT[(size_t)Kd * LAT_LDK + i] = 0.f;
+
+  // key range of this CTA and split
+  const int last_row = min(row0 + rows_cta, R) - 1;
+  const int n_keys = pos0 + last_row / a.heads + 1;                 // keys 0 .. n_keys-1 are visible to some row of the CTA
+  int per = (n_keys + (int)gridDim.y - 1) / (int)gridDim.y;
+  per = (per + LAT_BN - 1) / LAT_BN * LAT_BN;
+  const int j_begin = min(n_keys, (int)blockIdx.y * per), j_end = min(n_keys, j_begin + per);
+
+  int lim[LAT_RW];                                                  // last visible key of each row (-1: no such row)
+  float m[LAT_RW], l[LAT_RW], acc[LAT_RW][VI];
+#pragma unroll
+  for (int r = 0; r < LAT_RW; ++r) {
+    const int row = row0 + warp * LAT_RW + r;
+    lim[r] = row < R ? pos0 + row / a.heads : -1;
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+#pragma unroll
+    for (int i = 0; i < VI; ++i) acc[r][i] = 0.f;
+  }
+  const int warp_lim = max(max(lim[0], lim[1]), max(lim[2], lim[3]));
+  const float* qw = qs + (size_t)warp * LAT_RW * Kp;
+  float* pw = ps + (size_t)warp * LAT_RW * LAT_BN;
+
+  for (int jt = j_begin; jt < j_end; jt += LAT_BN) {
+    __syncthreads();                                                // the previous tile is consumed (and qs is written)
+    const int nk = min(LAT_BN, j_end - jt);
+    for (int i = threadIdx.x; i < LAT_BN * Kd; i += blockDim.x) {
+      const int j = i / Kd, d = i % Kd;
+      kT[(size_t)d * LAT_LDK + j] = j < nk ? ld_act(cache, (size_t)(jt + j) * Kd + d) : 0.f;
+    }
+    __syncthreads();
+    if (jt > warp_lim) continue;                                    // every key of the tile lies after this warp's rows
+    float s[LAT_RW] = {0.f, 0.f, 0.f, 0.f};
+    for (int d = 0; d < Kp; d += 4) {
+      const float k0 = kT[(size_t)d * LAT_LDK + lane], k1 = kT[(size_t)(d + 1) * LAT_LDK + lane];
+      const float k2 = kT[(size_t)(d + 2) * LAT_LDK + lane], k3 = kT[(size_t)(d + 3) * LAT_LDK + lane];
+#pragma unroll
+      for (int r = 0; r < LAT_RW; ++r) {
+        const float4 q4 = *reinterpret_cast<const float4*>(qw + (size_t)r * Kp + d);
+        s[r] = fmaf(q4.x, k0, fmaf(q4.y, k1, fmaf(q4.z, k2, fmaf(q4.w, k3, s[r]))));
+      }
+    }
+    const int j = jt + lane;
+#pragma unroll
+    for (int r = 0; r < LAT_RW; ++r) {
+      const bool seen = lane < nk && j <= lim[r];
+      const float sc = seen ? s[r] * a.scale : -INFINITY;
+      const float mn = fmaxf(m[r], warp_max(sc));
+      float p = 0.f, corr = 1.f;
+      if (mn > -INFINITY) {
+        p = seen ? expf(sc - mn) : 0.f;
+        corr = expf(m[r] - mn);                                     // m = -inf: 0
+      }
+      l[r] = l[r] * corr + warp_sum(p);
+      m[r] = mn;
+#pragma unroll
+      for (int i = 0; i < VI; ++i) acc[r][i] *= corr;
+      pw[r * LAT_BN + lane] = p;
+    }
+    __syncwarp();
+    for (int jj = 0; jj < LAT_BN; jj += 4) {
+      float4 p4[LAT_RW];
+#pragma unroll
+      for (int r = 0; r < LAT_RW; ++r) p4[r] = *reinterpret_cast<const float4*>(pw + r * LAT_BN + jj);
+#pragma unroll
+      for (int i = 0; i < VI; ++i) {
+        const int v = lane + 32 * i;
+        if (v < a.rank) {
+          const float* kv = kT + (size_t)v * LAT_LDK + jj;
+          const float c0 = kv[0], c1 = kv[1], c2 = kv[2], c3 = kv[3];
+#pragma unroll
+          for (int r = 0; r < LAT_RW; ++r)
+            acc[r][i] = fmaf(p4[r].x, c0, fmaf(p4[r].y, c1, fmaf(p4[r].z, c2, fmaf(p4[r].w, c3, acc[r][i]))));
+        }
+      }
+    }
+    __syncwarp();
+  }
+
+#pragma unroll
+  for (int r = 0; r < LAT_RW; ++r) {
+    const int row = row0 + warp * LAT_RW + r;
+    if (row >= R) continue;
+    const int t = row / a.heads, h = row % a.heads;
+    if (gridDim.y == 1) {
+      const float sink = a.sink[h];
+      const float M = fmaxf(m[r], sink);
+      const float e = expf(m[r] - M);                               // m = -inf (no key): 0
+      const float inv = e / (l[r] * e + expf(sink - M));
+      act_t* o = reinterpret_cast<act_t*>(a.out) + (size_t)t * a.ldo + (size_t)h * a.rank;
+#pragma unroll
+      for (int i = 0; i < VI; ++i) {
+        const int v = lane + 32 * i;
+        if (v < a.rank) st_act(o, v, acc[r][i] * inv);
+      }
+    } else {
+      float* w = a.work + ((size_t)blockIdx.y * R + row) * (size_t)(a.rank + 2);
+      if (lane == 0) {
+        w[0] = m[r];
+        w[1] = l[r];
+      }
+#pragma unroll
+      for (int i = 0; i < VI; ++i) {
+        const int v = lane + 32 * i;
+        if (v < a.rank) w[2 + v] = acc[r][i];
+      }
+    }
+  }
+}
+
+// Merges the key splits of a row and adds the sink.  One warp per row.
+template <typename act_t>
+__global__ void seq_latent_combine_kernel(const float* __restrict__ work, const float* __restrict__ sink, act_t* __restrict__ out, int ldo,
+                                          int R, int heads, int rank, int splits) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= R) return;
+  const int t = row / heads, h = row % heads;
+  const size_t stride = (size_t)(rank + 2);
+  float M = sink[h];
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, work[((size_t)s * R + row) * stride]);
+  float den = expf(sink[h] - M);
+  for (int s = 0; s < splits; ++s) {
+    const float* w = work + ((size_t)s * R + row) * stride;
+    if (w[0] > -INFINITY) den += w[1] * expf(w[0] - M);
+  }
+  act_t* o = out + (size_t)t * ldo + (size_t)h * rank;
+  for (int v = lane; v < rank; v += 32) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float* w = work + ((size_t)s * R + row) * stride;
+      if (w[0] > -INFINITY) acc += w[2 + v] * expf(w[0] - M);
+    }
+    st_act(o, v, acc / den);
+  }
+}
+
+static DynSmemCache g_lat_smem[8];
+
+template <typename act_t, int VI>
+static int launch_latent(const b2l_seq_latent_attn_args& a, int warps, size_t smem, int cache_id, cudaStream_t st) {
+  auto kern = seq_latent_attention_kernel<act_t, VI>;
+  if (smem > 48 * 1024) {
+    const int rc = ensure_dyn_smem(kern, smem, g_lat_smem[cache_id]);
+    if (rc != 0) return rc;
+  }
+  const int R = a.T * a.heads, rows_cta = warps * LAT_RW;
+  kern<<<dim3((R + rows_cta - 1) / rows_cta, a.splits), warps * 32, smem, st>>>(a);
+  return 0;
+}
+
+}  // namespace b2l
+
+using namespace b2l;
+
+extern "C" int b2l_seq_rope(const void* x, int ldx, int in_f32, const float* freq, int rot_dims, int interleaved, int rot_off,
+                            float mult, const int* meta, void* out, int ldo, int out_f32, int T, int heads, int size,
+                            int hsx, int hso, int act_dtype, b2l_stream_t stream) {
+  B2L_CHECK_ARG(x && meta && out, "b2l_seq_rope: null pointer");
+  B2L_CHECK_ARG(T >= 0 && heads > 0 && size > 0 && hsx >= size && hso >= size && ldx >= (heads - 1) * hsx + size && ldo >= (heads - 1) * hso + size,
+                "b2l_seq_rope: bad size");
+  B2L_CHECK_ARG(rot_dims >= 0 && rot_off >= 0 && rot_off + rot_dims <= size && rot_dims % 2 == 0 && (rot_dims == 0 || freq),
+                "b2l_seq_rope: bad rotation");
+  if (T == 0) return 0;
+  const int ids = T * heads, grid = (ids + 3) / 4;
+  cudaStream_t st = (cudaStream_t)stream;
+#define B2L_ROPE_GO(IN, OUT) \
+  seq_rope_kernel<IN, OUT><<<grid, 128, 0, st>>>((const IN*)x, ldx, freq, rot_dims, interleaved, rot_off, mult, meta, (OUT*)out, ldo, T, heads, size, hsx, hso)
+  B2L_SEQ_DISPATCH(act_dtype, {
+    if (in_f32 && out_f32) B2L_ROPE_GO(float, float);
+    else if (in_f32) B2L_ROPE_GO(float, act_t);
+    else if (out_f32) B2L_ROPE_GO(act_t, float);
+    else B2L_ROPE_GO(act_t, act_t);
+  });
+#undef B2L_ROPE_GO
+  B2L_LAUNCH_CHECK("seq_rope_kernel");
+  return 0;
+}
+
+extern "C" int b2l_seq_latent_prep(const float* proj, int ld, int q_off, int q_rank, const void* w_q, void* cq, int kv_off,
+                                   int rank, const void* w_kv, int rot_dim, const float* freq, int rot_dims, int interleaved,
+                                   float eps, const int* meta, void* cache, int max_pos, int T, int act_dtype,
+                                   b2l_stream_t stream) {
+  B2L_CHECK_ARG(proj && w_q && cq && w_kv && meta && cache, "b2l_seq_latent_prep: null pointer");
+  B2L_CHECK_ARG(T >= 0 && q_rank > 0 && rank > 0 && rot_dim >= 0 && max_pos > 0 && q_off >= 0 && kv_off >= 0 && ld >= q_off + q_rank &&
+                    ld >= kv_off + rank + rot_dim, "b2l_seq_latent_prep: bad size");
+  B2L_CHECK_ARG(rot_dims >= 0 && rot_dims <= rot_dim && rot_dims % 2 == 0 && (rot_dims == 0 || freq), "b2l_seq_latent_prep: bad rotation");
+  if (T == 0) return 0;
+  B2L_SEQ_DISPATCH(act_dtype, {
+    seq_latent_prep_kernel<act_t><<<T, 128, 0, (cudaStream_t)stream>>>(proj, ld, q_off, q_rank, (const act_t*)w_q, (act_t*)cq, kv_off, rank,
+                                                                      (const act_t*)w_kv, rot_dim, freq, rot_dims, interleaved, eps, meta,
+                                                                      (act_t*)cache, max_pos);
+  });
+  B2L_LAUNCH_CHECK("seq_latent_prep_kernel");
+  return 0;
+}
+
+extern "C" int b2l_seq_latent_attention_warps(int T, int heads) {
+  const int rows = T * heads;
+  int w = (rows + LAT_RW - 1) / LAT_RW;
+  return w < 1 ? 1 : (w > 8 ? 8 : w);
+}
+
+extern "C" int b2l_seq_latent_attention(const b2l_seq_latent_attn_args* a, b2l_stream_t stream) {
+  B2L_CHECK_ARG(a != nullptr, "b2l_seq_latent_attention: null args");
+  B2L_CHECK_ARG(a->q_lat && a->q_rot && a->cache && a->sink && a->meta && a->out, "b2l_seq_latent_attention: null pointer");
+  B2L_CHECK_ARG(a->T >= 0 && a->heads > 0 && a->rank > 0 && a->rot_dim >= 0 && a->max_pos > 0 && a->splits >= 1 && a->ldo >= a->heads * a->rank,
+                "b2l_seq_latent_attention: bad size");
+  B2L_CHECK_ARG(a->splits == 1 || a->work, "b2l_seq_latent_attention: key splits need a workspace");
+  B2L_CHECK_SUPPORTED(a->rank <= 512, "b2l_seq_latent_attention: latent size %d > 512", a->rank);
+  if (a->T == 0) return 0;
+  const int warps = b2l_seq_latent_attention_warps(a->T, a->heads);
+  const int Kd = a->rank + a->rot_dim, Kp = (Kd + 3) & ~3;
+  const size_t smem = sizeof(float) * ((size_t)Kp * LAT_LDK + (size_t)warps * LAT_RW * Kp + (size_t)warps * LAT_RW * LAT_BN);
+  B2L_CHECK_SUPPORTED(smem <= 220 * 1024, "b2l_seq_latent_attention: key size %d needs %zu bytes of shared memory", Kd, smem);
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc = 0;
+  B2L_SEQ_DISPATCH(a->act_dtype, {
+    const int base = sizeof(act_t) == 2 ? 0 : 4;
+    if (a->rank <= 64) rc = launch_latent<act_t, 2>(*a, warps, smem, base + 0, st);
+    else if (a->rank <= 128) rc = launch_latent<act_t, 4>(*a, warps, smem, base + 1, st);
+    else if (a->rank <= 256) rc = launch_latent<act_t, 8>(*a, warps, smem, base + 2, st);
+    else rc = launch_latent<act_t, 16>(*a, warps, smem, base + 3, st);
+  });
+  if (rc != 0) return rc;
+  B2L_LAUNCH_CHECK("seq_latent_attention_kernel");
+  if (a->splits > 1) {
+    const int R = a->T * a->heads;
+    B2L_SEQ_DISPATCH(a->act_dtype, {
+      seq_latent_combine_kernel<act_t><<<(R + 3) / 4, 128, 0, st>>>(a->work, a->sink, (act_t*)a->out, a->ldo, R, a->heads, a->rank, a->splits);
+    });
+    B2L_LAUNCH_CHECK("seq_latent_combine_kernel");
+  }
+  return 0;
+}

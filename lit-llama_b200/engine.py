@@ -65,6 +65,9 @@ class Engine:
             self.pool.acquire(request_id)
         self.pool.reserve(request_id, T)
         slot, pos0 = self.pool.slot(request_id), self.pool.position(request_id)
+        cap = getattr(self.model, "max_positions", 0)          # models that cache every position say how many fit a slot
+        if cap and pos0 + T > cap:
+            raise PoolFull(f"request {request_id!r} would reach position {pos0 + T}, a slot holds {cap}")
         self._meta.copy_(torch.tensor([slot, pos0], dtype=torch.int32))
         want = [T - 1] if want is None else list(want)
         if any(w < 0 or w >= T for w in want):
@@ -76,7 +79,7 @@ class Engine:
         else:
             tok = torch.tensor(list(tokens), dtype=torch.int64).to(self.device)
             w = torch.tensor(want, dtype=torch.int32).to(self.device) if want else None
-            ctx = StepContext(T, self._meta, self.pool.tensors, self.model.dtype)
+            ctx = StepContext(T, self._meta, self.pool.tensors, self.model.dtype, pos_hint=pos0)
             out = self.model.forward_portion(tok, ctx, w) if want else self._no_logits(tok, ctx)
         self.pool.advance(request_id, T)
         self.steps += 1

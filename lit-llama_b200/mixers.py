@@ -8,6 +8,10 @@ constants are constructor parameters.
     GatedLinearAttention S_t = diag(alpha_t) S_(t-1) + k_t v_t^T with a low-rank decay projection
     ParallelMixer        two mixers on the same input, one output product over their concatenated read-outs
     Mamba2Mixer          state-space duality layer: scalar decay per head, convolution on x | B | C, gated grouped norm
+    LatentAttention      causal softmax attention whose keys and values are linear images of one cached latent per position
+                         (+ one rotated key part shared by the heads), low-rank queries, a learned sink per head
+    RetentionMixer       linear attention with a fixed decay per head, rotated q / k, per-head unit-RMS read-out, silu gate
+    MoEFeedForward       routed gated experts: softmax scores, selection bias, expert groups, top-k, identity experts
 
 A mixer is built from a dict of weight tensors (`from_weights`) and runs one portion of one sequence:
 `forward(h, ctx)` with h [T, width] in the model's activation dtype.  Products go through torch (cuBLAS), as the
@@ -25,10 +29,12 @@ from .state import StateSpec
 
 
 class StepContext:
-    """One portion of one sequence: T tokens, the device pair {slot, first position} and the slot pool's tensors."""
+    """One portion of one sequence: T tokens, the device pair {slot, first position} and the slot pool's tensors.
+    `pos_hint` is the first position as the host knows it (None inside a captured step, which must not depend on it):
+    kernels never read it, it only sizes grids."""
 
-    def __init__(self, T: int, meta: torch.Tensor, state: Dict[str, torch.Tensor], dtype: torch.dtype) -> None:
-        self.T, self.meta, self.state, self.dtype = T, meta, state, dtype
+    def __init__(self, T: int, meta: torch.Tensor, state: Dict[str, torch.Tensor], dtype: torch.dtype, pos_hint: Optional[int] = None) -> None:
+        self.T, self.meta, self.state, self.dtype, self.pos_hint = T, meta, state, dtype, pos_hint
         self.act = S.act_code(dtype)
 
     @property
@@ -65,6 +71,13 @@ def stack_rows(parts: List[torch.Tensor]) -> Tuple[torch.Tensor, List[int]]:
 
 def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return F.linear(x, w)
+
+
+def linear_f32(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x W^T with the f32 accumulator kept (bf16 operands), or the plain f32 product."""
+    if x.dtype == torch.float32:
+        return F.linear(x, w)
+    return torch.mm(x, w.t(), out_dtype=torch.float32)
 
 
 # ------------------------------------------------------------------------------------------------ feed-forward
@@ -340,3 +353,206 @@ class ParallelMixer:
             at += n
             col += w
         return linear(out, self.w_o)
+
+
+# ------------------------------------------------------------------------------------------------ latent attention
+class LatentAttention:
+    """Causal softmax attention over a cached latent.
+
+        c_q = rmsnorm(W_dq h) w_q;  q = W_uq c_q, per head [dim unrotated | rot_dim rotated]
+        [c' | k_r] = W_dkv h;  c = rmsnorm(c') w_kv (kv_rank);  k_r rotated by position, shared by all heads
+        key_h = [W_uk,h c | k_r],  value_h = W_uv,h c,  score = q . key * scale
+        weights exp(s_j) / (exp(sink_h) + sum_j exp(s_j)),  y = W_o concat_h(sum_j weight_j value_j)
+
+    Only [c | k_r] is cached per position.  The attention runs in the latent space: the query is multiplied by W_uk
+    once (q' = W_uk,h^T q_h), scores are q' . c + q_r . k_r, the weighted sum of latents is mapped through W_uv
+    afterwards; every head reads the same cached row.  `rot`: {"base", "dims"} on the first `dims` entries of the
+    rotated part, pairs (2i, 2i+1) when `interleaved`."""
+
+    def __init__(self, name: str, W: Dict[str, torch.Tensor], p: str, *, heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int,
+                 kv_rank: int, scale: float, eps: float, rot: Optional[dict], max_positions: int, interleaved: bool = True) -> None:
+        if max_positions <= 0:
+            raise ValueError("latent attention caches every position: it needs max_positions")
+        self.name, self.H, self.dn, self.dr, self.dv, self.rq, self.rk = name, heads, dim, rot_dim, vdim, q_rank, kv_rank
+        self.scale, self.eps, self.max_positions, self.interleaved = float(scale), eps, int(max_positions), bool(interleaved)
+        self.w_in, (self.o_q, self.o_kv) = stack_rows([W[p + "dq"], W[p + "dkv"]])
+        assert W[p + "dq"].shape[0] == q_rank and W[p + "dkv"].shape[0] == kv_rank + rot_dim, "latent attention: down-projections do not fit"
+        self.q_norm, self.kv_norm = W[p + "dq.norm"].contiguous(), W[p + "dkv.norm"].contiguous()
+        self.w_uq = W[p + "uq"].contiguous()
+        assert self.w_uq.shape == (heads * (dim + rot_dim), q_rank), "latent attention: query up-projection does not fit"
+        self.w_uk = W[p + "uk"].reshape(heads, dim, kv_rank).contiguous()                      # q' = q_h W_uk,h
+        self.w_uv_t = W[p + "uv"].reshape(heads, vdim, kv_rank).transpose(1, 2).contiguous()   # value = o' W_uv,h^T
+        self.sink = W[p + "sink"].to(torch.float32).contiguous()
+        self.w_o = W[p + "o"].contiguous()
+        self.rot_dims, self.freq = 0, None
+        if rot and rot_dim:
+            self.rot_dims = int(rot["dims"])
+            f, _ = rope_frequencies(self.rot_dims, float(rot["base"]), rot.get("scaling"))
+            self.freq = f.to(self.w_o.device)
+
+    def state_specs(self) -> Dict[str, StateSpec]:
+        return {self.name + ".kv": StateSpec((self.max_positions, self.rk + self.dr), self.w_o.dtype, zero_on_acquire=False)}
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        lib, T, dev, H = S.lib(), ctx.T, h.device, self.H
+        proj = linear_f32(h, self.w_in)
+        cq = torch.empty((T, self.rq), dtype=h.dtype, device=dev)
+        cache = ctx.state[self.name + ".kv"]
+        S.check(lib.b2l_seq_latent_prep(_p(proj), proj.shape[1], self.o_q, self.rq, _p(self.q_norm), _p(cq), self.o_kv, self.rk, _p(self.kv_norm),
+                                        self.dr, _p(self.freq), self.rot_dims, int(self.interleaved), self.eps, _p(ctx.meta), _p(cache),
+                                        self.max_positions, T, ctx.act, ctx.stream), "b2l_seq_latent_prep")
+        dq = self.dn + self.dr
+        q = linear(cq, self.w_uq)                                                   # [T, H * (dim + rot_dim)]
+        qn = q.view(T, H, dq)[:, :, :self.dn].transpose(0, 1)                        # [H, T, dim]
+        q_lat = torch.bmm(qn, self.w_uk) if q.dtype == torch.float32 else torch.bmm(qn, self.w_uk, out_dtype=torch.float32)   # [H, T, rank] f32
+        q_rot = torch.empty((T, H, max(self.dr, 1)), dtype=torch.float32, device=dev)
+        if self.dr:
+            S.check(lib.b2l_seq_rope(_p(q, self.dn), H * dq, int(q.dtype == torch.float32), _p(self.freq), self.rot_dims, int(self.interleaved), 0,
+                                     1.0, _p(ctx.meta), _p(q_rot), H * self.dr, 1, T, H, self.dr, dq, self.dr, ctx.act, ctx.stream), "b2l_seq_rope")
+        o_lat = torch.empty((T, H * self.rk), dtype=h.dtype, device=dev)
+        # key splits: fill the machine when there are few rows; never a function of the position inside a captured step
+        n_keys = self.max_positions if ctx.pos_hint is None else min(self.max_positions, ctx.pos_hint + T)
+        warps = lib.b2l_seq_latent_attention_warps(T, H)
+        row_blocks = -(-T * H // (4 * warps))
+        splits = max(1, min(-(-296 // row_blocks), -(-n_keys // 64)))
+        work = torch.empty((splits, T * H, self.rk + 2), dtype=torch.float32, device=dev) if splits > 1 else None
+        a = S.LatentAttnArgs(q_lat=_p(q_lat), ldq_t=self.rk, ldq_h=T * self.rk, q_rot=_p(q_rot), ldr=max(self.dr, 1), rot_off=0, cache=_p(cache),
+                             max_pos=self.max_positions, sink=_p(self.sink), meta=_p(ctx.meta), out=_p(o_lat), ldo=H * self.rk, work=_p(work),
+                             scale=self.scale, T=T, heads=H, rank=self.rk, rot_dim=self.dr, splits=splits, act_dtype=ctx.act)
+        S.check(lib.b2l_seq_latent_attention(C.byref(a), ctx.stream), "b2l_seq_latent_attention")
+        v = torch.bmm(o_lat.view(T, H, self.rk).transpose(0, 1), self.w_uv_t)        # [H, T, vdim]
+        return linear(v.transpose(0, 1).reshape(T, H * self.dv), self.w_o)
+
+
+# ------------------------------------------------------------------------------------------------ retention
+class RetentionMixer:
+    """Linear attention with one fixed decay per head, no softmax and no denominator:
+
+        q, k rotated by position (first rot.dims entries of each head; entry i with entry i + dims/2), k times dim^-1/2
+        S_t = decay_h S_(t-1) + k_t v_t^T;  o_t = S_t^T q_t
+        y = W_o (concat_h(o_t,h / rms(o_t,h)) * silu(W_g h))
+
+    State per sequence: S (f32, heads x vdim x dim), zero at the start."""
+
+    def __init__(self, name: str, W: Dict[str, torch.Tensor], p: str, *, heads: int, dim: int, vdim: int, decay: List[float], eps: float,
+                 rot: Optional[dict], interleaved: bool = False) -> None:
+        self.name, self.H, self.K, self.V, self.eps, self.interleaved = name, heads, dim, vdim, eps, bool(interleaved)
+        if len(decay) != heads:
+            raise ValueError(f"retention: {len(decay)} decays for {heads} heads")
+        self.w_in, (self.o_q, self.o_k, self.o_v, self.o_g) = stack_rows([W[p + "q"], W[p + "k"], W[p + "v"], W[p + "g"]])
+        assert W[p + "q"].shape[0] == heads * dim and W[p + "v"].shape[0] == heads * vdim and W[p + "g"].shape[0] == heads * vdim
+        self.w_o = W[p + "o"].contiguous()
+        dev = self.w_o.device
+        self.decay = torch.tensor([float(d) for d in decay], dtype=torch.float32, device=dev)
+        self.ones = torch.ones(vdim, dtype=self.w_o.dtype, device=dev)
+        self.rot_dims, self.freq = 0, None
+        if rot:
+            self.rot_dims = int(rot["dims"])
+            f, _ = rope_frequencies(self.rot_dims, float(rot["base"]), rot.get("scaling"))
+            self.freq = f.to(dev)
+
+    def state_specs(self) -> Dict[str, StateSpec]:
+        return {self.name + ".S": StateSpec((self.H, self.V, self.K), torch.float32)}
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        lib, T, dev, H, K, V = S.lib(), ctx.T, h.device, self.H, self.K, self.V
+        proj = linear(h, self.w_in)
+        ld, f32in = proj.shape[1], int(proj.dtype == torch.float32)
+        qkv = torch.empty((T, 2 * H * K + H * V), dtype=torch.float32, device=dev)
+        n = qkv.shape[1]
+        for off_in, off_out, mult in ((self.o_q, 0, 1.0), (self.o_k, H * K, K ** -0.5)):
+            S.check(lib.b2l_seq_rope(_p(proj, off_in), ld, f32in, _p(self.freq), self.rot_dims, int(self.interleaved), 0, mult, _p(ctx.meta),
+                                     _p(qkv, off_out), n, 1, T, H, K, K, K, ctx.act, ctx.stream), "b2l_seq_rope")
+        S.check(lib.b2l_seq_cast_f32(_p(proj, self.o_v), ld, _p(qkv, 2 * H * K), n, T, H * V, ctx.act, ctx.stream), "b2l_seq_cast_f32")
+        o = torch.empty((T, H * V), dtype=torch.float32, device=dev)
+        _scan(ctx, q=_p(qkv), ldq=n, k=_p(qkv, H * K), ldk=n, v=_p(qkv, 2 * H * K), ldv=n, q_mult=1.0, decay=_p(self.decay), ldd=0,
+              per_channel=False, state=ctx.state[self.name + ".S"], out=_p(o), ldo=H * V, heads=H, qk_heads=H, K=K, V=V)
+        y = torch.empty((T, H * V), dtype=h.dtype, device=dev)
+        S.check(lib.b2l_seq_group_norm_gate(_p(o), H * V, _p(self.ones), 1, _p(proj, self.o_g), ld, S.ACT_SILU, 0, self.eps, 1.0, _p(y), H * V, T,
+                                            H * V, V, ctx.act, ctx.stream), "b2l_seq_group_norm_gate")
+        return linear(y, self.w_o)
+
+
+# ------------------------------------------------------------------------------------------------ routed experts
+class MoEFeedForward:
+    """y = sum over the chosen experts of weight_e * expert_e(h).
+
+        s = softmax(W_router h) over all experts (f32);  choice = s + correction (steers the choice only)
+        experts form `groups` equal groups of neighbours; only experts of the `keep` groups with the largest best
+        choice score can be chosen; the `top` largest choice scores win; weight = s / (sum of the chosen s + 1e-20)
+        expert e < experts: W_down (act(W_gate h) * (W_up h));  the last `identity` outputs of the router: h itself
+
+    A few tokens (also the captured single-token step) run with the expert index read on the device; longer portions
+    sort the assignments by expert and run one pair of products per expert that received tokens."""
+
+    SMALL = 4
+
+    def __init__(self, W: Dict[str, torch.Tensor], p: str, *, experts: int, identity: int, top: int, groups: int, keep: int, ff: int,
+                 act: str = "silu") -> None:
+        self.E, self.I, self.top, self.groups, self.keep, self.ff = int(experts), int(identity), int(top), int(groups), int(keep), int(ff)
+        self.n = self.E + self.I
+        if self.n % self.groups or not (1 <= self.keep <= self.groups) or self.keep * (self.n // self.groups) < self.top:
+            raise ValueError("routed experts: groups / keep / top do not fit the expert count")
+        self.act = GatedMLP.ACTS[act]
+        if self.act != S.ACT_SILU:
+            raise ValueError("routed experts: the device-indexed products implement silu only")
+        self.w_router = W[p + "router"].to(torch.float32).contiguous()
+        assert self.w_router.shape[0] == self.n, "routed experts: the router does not have experts + identity outputs"
+        self.correction = W[p + "correction"].to(torch.float32).contiguous() if (p + "correction") in W else None
+        dev, dt = self.w_router.device, W[p + "router"].dtype
+        if self.E:
+            self.w_gu = torch.stack([torch.cat([W[f"{p}e{e}.gate"], W[f"{p}e{e}.up"]], dim=0) for e in range(self.E)]).contiguous()
+            self.w_down = torch.stack([W[f"{p}e{e}.down"] for e in range(self.E)]).contiguous()
+            assert self.w_gu.shape[1] == 2 * self.ff, "routed experts: expert size does not fit"
+        else:
+            self.w_gu = self.w_down = torch.zeros(0, dtype=dt, device=dev)
+        self.last_idx: Optional[torch.Tensor] = None       # the routing of the last call (tests, diagnostics)
+
+    def state_specs(self) -> Dict[str, StateSpec]:
+        return {}
+
+    def route(self, h: torch.Tensor, ctx: StepContext) -> Tuple[torch.Tensor, torch.Tensor]:
+        lib, T, dev, D = S.lib(), ctx.T, h.device, h.shape[1]
+        if torch.backends.cuda.matmul.allow_tf32:
+            raise RuntimeError("router logits need true 32-bit products: torch.backends.cuda.matmul.allow_tf32 is on")
+        if h.dtype == torch.float32:
+            h32 = h
+        else:
+            h32 = torch.empty((T, D), dtype=torch.float32, device=dev)
+            S.check(lib.b2l_seq_cast_f32(_p(h), D, _p(h32), D, T, D, ctx.act, ctx.stream), "b2l_seq_cast_f32")
+        z = F.linear(h32, self.w_router)
+        idx = torch.empty((T, self.top), dtype=torch.int32, device=dev)
+        wgt = torch.empty((T, self.top), dtype=torch.float32, device=dev)
+        S.check(lib.b2l_seq_moe_route(_p(z), self.n, _p(self.correction), self.n, self.groups, self.keep, self.top, _p(idx), _p(wgt), T,
+                                      ctx.stream), "b2l_seq_moe_route")
+        self.last_idx = idx
+        return idx, wgt
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        lib, T, dev, D, E, top, ff = S.lib(), ctx.T, h.device, h.shape[1], self.E, self.top, self.ff
+        idx, wgt = self.route(h, ctx)
+        y = torch.empty((T, D), dtype=h.dtype, device=dev)
+        N = T * top
+        if T <= self.SMALL or E == 0:
+            mid = torch.empty((N, ff), dtype=h.dtype, device=dev)
+            S.check(lib.b2l_seq_moe_experts_small(_p(h), D, _p(self.w_gu) if E else None, _p(self.w_down) if E else None, _p(idx), _p(wgt), _p(mid),
+                                                  _p(y), D, T, D, ff, E, top, ctx.act, ctx.stream), "b2l_seq_moe_experts_small")
+            return y
+        meta = torch.empty((2 * (E + 1) + 2 * N,), dtype=torch.int32, device=dev)
+        offsets, cursor, perm, inv = meta[:E + 1], meta[E + 1:2 * E + 2], meta[2 * E + 2:2 * E + 2 + N], meta[2 * E + 2 + N:]
+        S.check(lib.b2l_seq_moe_sort(_p(idx), N, E, _p(offsets), _p(cursor), _p(perm), _p(inv), ctx.stream), "b2l_seq_moe_sort")
+        xg = torch.empty((N, D), dtype=h.dtype, device=dev)
+        S.check(lib.b2l_seq_moe_gather(_p(h), D, _p(perm), _p(offsets, E), top, _p(xg), N, D, ctx.act, ctx.stream), "b2l_seq_moe_gather")
+        off = offsets.cpu().tolist()                                   # the one host read of a long portion
+        gu = torch.empty((N, 2 * ff), dtype=h.dtype, device=dev)
+        for e in range(E):
+            if off[e + 1] > off[e]:
+                torch.mm(xg[off[e]:off[e + 1]], self.w_gu[e].t(), out=gu[off[e]:off[e + 1]])
+        mid = torch.empty((N, ff), dtype=h.dtype, device=dev)
+        S.check(lib.b2l_seq_gated_act(_p(gu), 2 * ff, _p(mid), off[E], ff, self.act, ctx.act, ctx.stream), "b2l_seq_gated_act")
+        yg = torch.empty((N, D), dtype=h.dtype, device=dev)
+        for e in range(E):
+            if off[e + 1] > off[e]:
+                torch.mm(mid[off[e]:off[e + 1]], self.w_down[e].t(), out=yg[off[e]:off[e + 1]])
+        S.check(lib.b2l_seq_moe_combine(_p(yg), _p(inv), _p(wgt), _p(h), D, _p(y), D, T, D, top, ctx.act, ctx.stream), "b2l_seq_moe_combine")
+        return y

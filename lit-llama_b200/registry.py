@@ -28,6 +28,13 @@ def _load_lugovik(model_dir: str, dtype: torch.dtype, device: torch.device, max_
     return lugovik.load(model_dir, dtype=dtype, device=device, max_positions=max_positions)
 
 
+@register("Zenasun")
+def _load_zenasun(model_dir: str, dtype: torch.dtype, device: torch.device, max_positions: int, config: dict):
+    from . import zenasun
+
+    return zenasun.load(model_dir, dtype=dtype, device=device, max_positions=max_positions)
+
+
 @register("LLaMA")
 def _load_llama(model_dir: str, dtype: torch.dtype, device: torch.device, max_positions: int, config: dict):
     """config.json: {"architecture": "LLaMA", "name": "7B" | sizes..., "quantize": null | "gptq.int4" | ..., "checkpoint": file}."""
