@@ -116,7 +116,8 @@ def model(tokens, config, weights, capture=None):
     eps = config["norm"]["eps"]
     x = W["embed"][torch.tensor(tokens)] * config["embedding"]["scale"]
     for i, layer in enumerate(config["layers"]):
-        p = "l%d." % layer.get("weights_of", i)
+        j = layer.get("weights_of")
+        p = "l%d." % (i if j is None else j)
         h1 = norm_around_zero(x, W[p + "norm1"], eps)
         if layer["type"] == "latent_attention":
             y = latent_attention(h1, W, p + "mix.", layer["mixer"], eps)
