@@ -197,3 +197,41 @@ def load(model_dir: str, dtype: torch.dtype = torch.bfloat16, device: Optional[t
     config = ZenasunConfig.from_json(os.path.join(model_dir, "config.json"))
     weights = read_safetensors(os.path.join(model_dir, "model.safetensors"), device=device, float_dtype=dtype)
     return Zenasun(config, weights, max_positions=max_positions)
+
+
+def random_weights(cfg: dict, device, dtype: torch.dtype = torch.bfloat16, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random tensors with the family's names and shapes (projections ~ N(0, 1/in), norm weights around zero), for
+    benchmarks and smoke runs."""
+    import math
+
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    D, W = cfg["width"], {}
+
+    def lin(o, i):
+        return (torch.randn(o, i, generator=g) / math.sqrt(i)).to(device, dtype)
+
+    def vec(n, mean=0.0, std=0.1):
+        return (mean + std * torch.randn(n, generator=g)).to(device, dtype)
+
+    W["embed"], W["final.norm"] = (torch.randn(cfg["vocab"], D, generator=g) / math.sqrt(D)).to(device, dtype), vec(D)
+    for i, layer in enumerate(cfg["layers"]):
+        if layer.get("weights_of") is not None:
+            continue
+        p, m, c = f"l{i}.", f"l{i}.mix.", layer["mixer"]
+        W[p + "norm1"] = vec(D)
+        if layer["type"] == "latent_attention":
+            H, dn, dr, dv, rq, rk = c["heads"], c["dim"], c.get("rot_dim", 0), c["vdim"], c["q_rank"], c["kv_rank"]
+            W[m + "dq"], W[m + "dq.norm"], W[m + "uq"] = lin(rq, D), vec(rq, 1.0), lin(H * (dn + dr), rq)
+            W[m + "dkv"], W[m + "dkv.norm"] = lin(rk + dr, D), vec(rk, 1.0)
+            W[m + "uk"], W[m + "uv"], W[m + "sink"], W[m + "o"] = lin(H * dn, rk), lin(H * dv, rk), vec(H, 0.0, 1.0), lin(D, H * dv)
+        else:
+            H, K, V = c["heads"], c["dim"], c["vdim"]
+            W[m + "q"], W[m + "k"], W[m + "v"], W[m + "g"], W[m + "o"] = lin(H * K, D), lin(H * K, D), lin(H * V, D), lin(H * V, D), lin(D, H * V)
+        if layer.get("mlp"):
+            r, ff = layer["mlp"]["router"], layer["mlp"]["expert"]["ff"]
+            n = r["experts"] + r.get("identity", 0)
+            W[p + "norm2"], W[p + "mlp.router"], W[p + "mlp.correction"] = vec(D), lin(n, D), vec(n, 0.0, 0.01)
+            for e in range(r["experts"]):
+                q = f"{p}mlp.e{e}."
+                W[q + "gate"], W[q + "up"], W[q + "down"] = lin(ff, D), lin(ff, D), lin(D, ff)
+    return W
