@@ -164,27 +164,34 @@ int b2l_seq_latent_prep(const float* proj, int ld, int q_off, int q_rank, const 
                         const void* w_kv, int rot_dim, const float* freq, int rot_dims, int interleaved, float eps,
                         const int* meta, void* cache, int max_pos, int T, int act_dtype, b2l_stream_t stream);
 
-/* Causal softmax attention of T x heads query rows over the cached positions 0 .. pos0 + t, in the latent space:
- *   score = (q_lat . latent_j + q_rot . rotated_key_j) * scale;  weights exp(score_j) / (exp(sink[h]) + sum_j exp(score_j))
- *   out[t, h*rank : (h+1)*rank] = sum_j weight_j latent_j
- * q_lat is the query already multiplied by the key up-projection (f32, element [t][h][d] at t*ldq_t + h*ldq_h + d),
- * q_rot the rotated query part (f32, row (t, h) at (t*heads + h)*ldr + rot_off).  The cache must already hold the
- * portion's own positions (b2l_seq_latent_prep).  `splits` > 1 cuts the keys into that many ranges that run in
- * parallel and are merged afterwards; it needs work: f32 [splits][T*heads][rank + 2].  The grid does not depend on
- * the position, so a captured single-token step replays anywhere. */
+/* Causal softmax attention with a learned sink per head over keys 0 .. pos0 + t:
+ *   weights exp(score_j) / (exp(sink[h]) + sum_j exp(score_j)),  score = (q . key_j[score_off:]) * scale
+ *   out[t, h*vdim : (h+1)*vdim] = sum_j weight_j key_j[0 : vdim]
+ * A key row is [A (n_a entries) | B (n_b entries)]: A belongs to a key group (row j at key_a + slot*slot_stride_a +
+ * group*hska + j*ldka), B is shared by all groups (key_b + slot*slot_stride_b + j*ldkb); heads_per_group consecutive
+ * heads share a group.  The query of row (t, h) is [q_a (n_a - score_off entries) | q_b (n_b entries)], f32, at
+ * q_x + t*ldqx_t + h*ldqx_h.
+ *   latent form:   heads_per_group = heads, A = the cached latent (n_a = vdim = rank, score_off = 0), B = the cached
+ *                  rotated key; q_a is the query already multiplied by the key up-projection; out is the weighted
+ *                  latent, still to be mapped to the value space.
+ *   expanded form: heads_per_group = 1, A = [value_h | unrotated key_h] of every position (score_off = vdim).
+ * The cache must already hold the portion's own positions (b2l_seq_latent_prep).  `splits` > 1 cuts the keys into
+ * that many ranges that run in parallel and are merged afterwards; it needs work: f32 [splits][T*heads][vdim + 2].
+ * The grid does not depend on the position, so a captured single-token step replays anywhere. */
 typedef struct {
-  const float* q_lat; long long ldq_t; long long ldq_h;
-  const float* q_rot; int ldr; int rot_off;
-  const void* cache; int max_pos;
+  const float* q_a; long long ldqa_t; long long ldqa_h;
+  const float* q_b; long long ldqb_t; long long ldqb_h;
+  const void* key_a; long long ldka; long long hska; long long slot_stride_a;
+  const void* key_b; long long ldkb; long long slot_stride_b;
   const float* sink;               /* f32 [heads] */
   const int* meta;
   void* out; int ldo;              /* act [T, ldo] */
   float* work;
   float scale;
-  int T, heads, rank, rot_dim, splits, act_dtype;
+  int T, heads, heads_per_group, n_a, n_b, vdim, score_off, splits, act_dtype;
 } b2l_seq_latent_attn_args;
 int b2l_seq_latent_attention(const b2l_seq_latent_attn_args* a, b2l_stream_t stream);
-int b2l_seq_latent_attention_warps(int T, int heads);    /* warps per CTA the call will use: 4 rows per warp */
+int b2l_seq_latent_attention_warps(int T, int heads_per_group);    /* warps per CTA that own rows: 4 rows per warp */
 
 /* ---- mixture of experts ----
  * Router, per token, from f32 logits [T, ld] over n experts: s = softmax(logits); choice = s + correction (f32 [n],

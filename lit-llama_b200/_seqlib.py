@@ -48,15 +48,17 @@ class AttnArgs(C.Structure):
 
 class LatentAttnArgs(C.Structure):
     _fields_ = [
-        ("q_lat", c_void_p), ("ldq_t", C.c_longlong), ("ldq_h", C.c_longlong),
-        ("q_rot", c_void_p), ("ldr", c_int), ("rot_off", c_int),
-        ("cache", c_void_p), ("max_pos", c_int),
+        ("q_a", c_void_p), ("ldqa_t", C.c_longlong), ("ldqa_h", C.c_longlong),
+        ("q_b", c_void_p), ("ldqb_t", C.c_longlong), ("ldqb_h", C.c_longlong),
+        ("key_a", c_void_p), ("ldka", C.c_longlong), ("hska", C.c_longlong), ("slot_stride_a", C.c_longlong),
+        ("key_b", c_void_p), ("ldkb", C.c_longlong), ("slot_stride_b", C.c_longlong),
         ("sink", c_void_p),
         ("meta", c_void_p),
         ("out", c_void_p), ("ldo", c_int),
         ("work", c_void_p),
         ("scale", c_float),
-        ("T", c_int), ("heads", c_int), ("rank", c_int), ("rot_dim", c_int), ("splits", c_int), ("act_dtype", c_int),
+        ("T", c_int), ("heads", c_int), ("heads_per_group", c_int), ("n_a", c_int), ("n_b", c_int), ("vdim", c_int), ("score_off", c_int),
+        ("splits", c_int), ("act_dtype", c_int),
     ]
 
 

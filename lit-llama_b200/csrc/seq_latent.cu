@@ -1,10 +1,14 @@
 // Latent attention: keys and values of every head are linear images of one cached latent vector per position, plus
-// one rotated key part shared by all heads.  Only [latent | rotated key] is cached.  The attention runs in the
-// latent space ("absorbed" form): with q' = W_uk^T q_unrotated per head,
-//     score(i, j) = (q'_i . c_j + q_rot_i . k_rot_j) * scale,     o'_i = sum_j weight(i, j) c_j,
-// and the caller maps o' to the value space (W_uv) afterwards.  All heads of all queries are rows over the same
-// keys, so one key tile in shared memory serves every row of a CTA.  Softmax has one learned sink per head in the
-// denominator (exp(sink_h), no key, no value).  Scores, weights and accumulators are f32.
+// one rotated key part shared by all heads.  Only [latent | rotated key] is cached.  One kernel serves two forms:
+//  - latent ("absorbed") form, for single tokens and short portions: with q' = W_uk^T q_unrotated per head,
+//        score(i, j) = (q'_i . c_j + q_rot_i . k_rot_j) * scale,     o'_i = sum_j weight(i, j) c_j,
+//    and the caller maps o' to the value space (W_uv) afterwards.  All heads of all queries are rows over the same
+//    cached rows, so one key tile in shared memory serves every row of a CTA and the cache is read once;
+//  - expanded form, for long portions: the caller expands [value_h | key_h] of every cached position with one
+//    product, and every head attends over its own rows plus the shared rotated part: 3-4 times fewer operations
+//    per (query, key) pair when the latent is several times wider than a head.
+// Softmax has one learned sink per head in the denominator (exp(sink_h), no key, no value).  Scores, weights and
+// accumulators are f32.
 #include "seq_common.cuh"
 
 namespace b2l {
@@ -81,39 +85,51 @@ __global__ void __launch_bounds__(128) seq_latent_prep_kernel(const float* __res
 constexpr int LAT_RW = 4;       // rows (query, head) per warp
 constexpr int LAT_BN = 32;      // keys per tile: one per lane
 constexpr int LAT_LDK = 33;     // padded key count of the transposed tile
+constexpr int LAT_THREADS = 256;
 
-// Rows r = t * heads + h.  A warp owns LAT_RW consecutive rows, a CTA blockDim/32 warps; grid.y splits the keys.
-// Shared: kT[Kp][33] (the key tile transposed, f32), qs[rows][Kp], ps[rows][32].  Scores: lane j owns key j of the
-// tile (q read as broadcast float4, kT conflict-free).  Values: lane owns latent entries lane + 32 i (weights read
+// A key row is [A (n_a entries) | B (n_b entries)]: A per key group, B shared by all groups (the rotated key part).
+// Scores use the entries from score_off on, values are the first vdim entries of A.  Two uses:
+//   latent form:   one group, A = cached latent, B = cached rotated key, score_off 0, vdim = rank, every head of every
+//                  query is a row over the same keys (heads_per_group = heads);
+//   expanded form: a group per head (grid.z), A = [value_h | unrotated key_h] expanded from the latent for this call,
+//                  score_off = vdim, heads_per_group = 1.
+// Rows of a group: r = t * heads_per_group + (h % heads_per_group).  The first `row_warps` warps own LAT_RW
+// consecutive rows each, every warp of the CTA helps to load key tiles; grid.y splits the keys.
+// Shared: kT[Kp][33] (the key tile transposed, f32), qs[rows][Qp], ps[rows][32].  Scores: lane j owns key j of the
+// tile (q read as broadcast float4, kT conflict-free).  Values: lane owns value entries lane + 32 i (weights read
 // as broadcast float4, kT with stride 33 conflict-free).
 template <typename act_t, int VI>
-__global__ void __launch_bounds__(256) seq_latent_attention_kernel(b2l_seq_latent_attn_args a) {
+__global__ void __launch_bounds__(LAT_THREADS) seq_latent_attention_kernel(b2l_seq_latent_attn_args a, int row_warps) {
   extern __shared__ __align__(16) float lat_smem[];
-  const int Kd = a.rank + a.rot_dim, Kp = (Kd + 3) & ~3;
+  const int Kall = a.n_a + a.n_b, Kp = (Kall + 3) & ~3;
+  const int s0 = a.score_off & ~3, Qp = Kp - s0;                       // scores run over d in [s0, Kp), q is zero below score_off
   const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int rows_cta = nw * LAT_RW, R = a.T * a.heads;
+  const int hpg = a.heads_per_group, group = blockIdx.z;
+  const int rows_cta = row_warps * LAT_RW, R = a.T * hpg;
   float* kT = lat_smem;
   float* qs = kT + (size_t)Kp * LAT_LDK;
-  float* ps = qs + (size_t)rows_cta * Kp;
+  float* ps = qs + (size_t)rows_cta * Qp;
   const int slot = a.meta[0], pos0 = a.meta[1];
   const int row0 = blockIdx.x * rows_cta;
-  const act_t* cache = reinterpret_cast<const act_t*>(a.cache) + (size_t)slot * a.max_pos * Kd;
+  const act_t* key_a = reinterpret_cast<const act_t*>(a.key_a) + (size_t)slot * a.slot_stride_a + (size_t)group * a.hska;
+  const act_t* key_b = reinterpret_cast<const act_t*>(a.key_b) + (size_t)slot * a.slot_stride_b;
 
-  // queries of this CTA's rows -> shared (zero beyond the row count and in the padding)
-  for (int i = threadIdx.x; i < rows_cta * Kp; i += blockDim.x) {
-    const int rl = i / Kp, d = i % Kp, r = row0 + rl;
+  // queries of this CTA's rows -> shared (zero beyond the row count, below score_off and in the padding)
+  for (int i = threadIdx.x; i < rows_cta * Qp; i += blockDim.x) {
+    const int rl = i / Qp, d = s0 + i % Qp, r = row0 + rl;
     float v = 0.f;
-    if (r < R && d < Kd) {
-      const int t = r / a.heads, h = r % a.heads;
-      v = d < a.rank ? a.q_lat[(size_t)t * a.ldq_t + (size_t)h * a.ldq_h + d] : a.q_rot[((size_t)t * a.heads + h) * a.ldr + a.rot_off + (d - a.rank)];
+    if (r < R && d >= a.score_off && d < Kall) {
+      const int t = r / hpg, h = group * hpg + r % hpg;
+      v = d < a.n_a ? a.q_a[(size_t)t * a.ldqa_t + (size_t)h * a.ldqa_h + (d - a.score_off)]
+                    : a.q_b[(size_t)t * a.ldqb_t + (size_t)h * a.ldqb_h + (d - a.n_a)];
     }
     qs[i] = v;
   }
-  for (int i = threadIdx.x; i < (Kp - Kd) * LAT_LDK; i += blockDim.x) kT[(size_t)Kd * LAT_LDK + i] = 0.f;
+  for (int i = threadIdx.x; i < (Kp - Kall) * LAT_LDK; i += blockDim.x) kT[(size_t)Kall * LAT_LDK + i] = 0.f;
 
   // key range of this CTA and split
   const int last_row = min(row0 + rows_cta, R) - 1;
-  const int n_keys = pos0 + last_row / a.heads + 1;                 // keys 0 .. n_keys-1 are visible to some row of the CTA
+  const int n_keys = pos0 + last_row / hpg + 1;                     // keys 0 .. n_keys-1 are visible to some row of the CTA
   int per = (n_keys + (int)gridDim.y - 1) / (int)gridDim.y;
   per = (per + LAT_BN - 1) / LAT_BN * LAT_BN;
   const int j_begin = min(n_keys, (int)blockIdx.y * per), j_end = min(n_keys, j_begin + per);
@@ -123,32 +139,38 @@ __global__ void __launch_bounds__(256) seq_latent_attention_kernel(b2l_seq_laten
 #pragma unroll
   for (int r = 0; r < LAT_RW; ++r) {
     const int row = row0 + warp * LAT_RW + r;
-    lim[r] = row < R ? pos0 + row / a.heads : -1;
+    lim[r] = (warp < row_warps && row < R) ? pos0 + row / hpg : -1;
     m[r] = -INFINITY;
     l[r] = 0.f;
 #pragma unroll
     for (int i = 0; i < VI; ++i) acc[r][i] = 0.f;
   }
   const int warp_lim = max(max(lim[0], lim[1]), max(lim[2], lim[3]));
-  const float* qw = qs + (size_t)warp * LAT_RW * Kp;
-  float* pw = ps + (size_t)warp * LAT_RW * LAT_BN;
+  const int wq = min(warp, row_warps - 1);                          // loader-only warps never read these
+  const float* qw = qs + (size_t)wq * LAT_RW * Qp;
+  float* pw = ps + (size_t)wq * LAT_RW * LAT_BN;
 
   for (int jt = j_begin; jt < j_end; jt += LAT_BN) {
     __syncthreads();                                                // the previous tile is consumed (and qs is written)
     const int nk = min(LAT_BN, j_end - jt);
-    for (int i = threadIdx.x; i < LAT_BN * Kd; i += blockDim.x) {
-      const int j = i / Kd, d = i % Kd;
-      kT[(size_t)d * LAT_LDK + j] = j < nk ? ld_act(cache, (size_t)(jt + j) * Kd + d) : 0.f;
+    for (int j = warp; j < LAT_BN; j += nw) {                       // a warp per key row, lanes along the row
+      const bool ok = j < nk;
+      const act_t* pa = key_a + (size_t)(jt + j) * a.ldka;
+      const act_t* pb = key_b + (size_t)(jt + j) * a.ldkb;
+#pragma unroll 4
+      for (int d = lane; d < a.n_a; d += 32) kT[(size_t)d * LAT_LDK + j] = ok ? ld_act(pa, d) : 0.f;
+#pragma unroll 2
+      for (int d = lane; d < a.n_b; d += 32) kT[(size_t)(a.n_a + d) * LAT_LDK + j] = ok ? ld_act(pb, d) : 0.f;
     }
     __syncthreads();
     if (jt > warp_lim) continue;                                    // every key of the tile lies after this warp's rows
     float s[LAT_RW] = {0.f, 0.f, 0.f, 0.f};
-    for (int d = 0; d < Kp; d += 4) {
+    for (int d = s0; d < Kp; d += 4) {
       const float k0 = kT[(size_t)d * LAT_LDK + lane], k1 = kT[(size_t)(d + 1) * LAT_LDK + lane];
       const float k2 = kT[(size_t)(d + 2) * LAT_LDK + lane], k3 = kT[(size_t)(d + 3) * LAT_LDK + lane];
 #pragma unroll
       for (int r = 0; r < LAT_RW; ++r) {
-        const float4 q4 = *reinterpret_cast<const float4*>(qw + (size_t)r * Kp + d);
+        const float4 q4 = *reinterpret_cast<const float4*>(qw + (size_t)r * Qp + (d - s0));
         s[r] = fmaf(q4.x, k0, fmaf(q4.y, k1, fmaf(q4.z, k2, fmaf(q4.w, k3, s[r]))));
       }
     }
@@ -177,7 +199,7 @@ __global__ void __launch_bounds__(256) seq_latent_attention_kernel(b2l_seq_laten
 #pragma unroll
       for (int i = 0; i < VI; ++i) {
         const int v = lane + 32 * i;
-        if (v < a.rank) {
+        if (v < a.vdim) {
           const float* kv = kT + (size_t)v * LAT_LDK + jj;
           const float c0 = kv[0], c1 = kv[1], c2 = kv[2], c3 = kv[3];
 #pragma unroll
@@ -189,24 +211,25 @@ __global__ void __launch_bounds__(256) seq_latent_attention_kernel(b2l_seq_laten
     __syncwarp();
   }
 
+  if (warp >= row_warps) return;
 #pragma unroll
   for (int r = 0; r < LAT_RW; ++r) {
     const int row = row0 + warp * LAT_RW + r;
     if (row >= R) continue;
-    const int t = row / a.heads, h = row % a.heads;
+    const int t = row / hpg, h = group * hpg + row % hpg;
     if (gridDim.y == 1) {
       const float sink = a.sink[h];
       const float M = fmaxf(m[r], sink);
       const float e = expf(m[r] - M);                               // m = -inf (no key): 0
       const float inv = e / (l[r] * e + expf(sink - M));
-      act_t* o = reinterpret_cast<act_t*>(a.out) + (size_t)t * a.ldo + (size_t)h * a.rank;
+      act_t* o = reinterpret_cast<act_t*>(a.out) + (size_t)t * a.ldo + (size_t)h * a.vdim;
 #pragma unroll
       for (int i = 0; i < VI; ++i) {
         const int v = lane + 32 * i;
-        if (v < a.rank) st_act(o, v, acc[r][i] * inv);
+        if (v < a.vdim) st_act(o, v, acc[r][i] * inv);
       }
     } else {
-      float* w = a.work + ((size_t)blockIdx.y * R + row) * (size_t)(a.rank + 2);
+      float* w = a.work + ((size_t)blockIdx.y * a.T * a.heads + (size_t)t * a.heads + h) * (size_t)(a.vdim + 2);
       if (lane == 0) {
         w[0] = m[r];
         w[1] = l[r];
@@ -214,20 +237,20 @@ __global__ void __launch_bounds__(256) seq_latent_attention_kernel(b2l_seq_laten
 #pragma unroll
       for (int i = 0; i < VI; ++i) {
         const int v = lane + 32 * i;
-        if (v < a.rank) w[2 + v] = acc[r][i];
+        if (v < a.vdim) w[2 + v] = acc[r][i];
       }
     }
   }
 }
 
-// Merges the key splits of a row and adds the sink.  One warp per row.
+// Merges the key splits of a row and adds the sink.  One warp per row (t, h).
 template <typename act_t>
 __global__ void seq_latent_combine_kernel(const float* __restrict__ work, const float* __restrict__ sink, act_t* __restrict__ out, int ldo,
-                                          int R, int heads, int rank, int splits) {
+                                          int R, int heads, int vdim, int splits) {
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= R) return;
   const int t = row / heads, h = row % heads;
-  const size_t stride = (size_t)(rank + 2);
+  const size_t stride = (size_t)(vdim + 2);
   float M = sink[h];
   for (int s = 0; s < splits; ++s) M = fmaxf(M, work[((size_t)s * R + row) * stride]);
   float den = expf(sink[h] - M);
@@ -235,8 +258,8 @@ __global__ void seq_latent_combine_kernel(const float* __restrict__ work, const 
     const float* w = work + ((size_t)s * R + row) * stride;
     if (w[0] > -INFINITY) den += w[1] * expf(w[0] - M);
   }
-  act_t* o = out + (size_t)t * ldo + (size_t)h * rank;
-  for (int v = lane; v < rank; v += 32) {
+  act_t* o = out + (size_t)t * ldo + (size_t)h * vdim;
+  for (int v = lane; v < vdim; v += 32) {
     float acc = 0.f;
     for (int s = 0; s < splits; ++s) {
       const float* w = work + ((size_t)s * R + row) * stride;
@@ -249,14 +272,14 @@ __global__ void seq_latent_combine_kernel(const float* __restrict__ work, const 
 static DynSmemCache g_lat_smem[8];
 
 template <typename act_t, int VI>
-static int launch_latent(const b2l_seq_latent_attn_args& a, int warps, size_t smem, int cache_id, cudaStream_t st) {
+static int launch_latent(const b2l_seq_latent_attn_args& a, int row_warps, size_t smem, int cache_id, cudaStream_t st) {
   auto kern = seq_latent_attention_kernel<act_t, VI>;
   if (smem > 48 * 1024) {
     const int rc = ensure_dyn_smem(kern, smem, g_lat_smem[cache_id]);
     if (rc != 0) return rc;
   }
-  const int R = a.T * a.heads, rows_cta = warps * LAT_RW;
-  kern<<<dim3((R + rows_cta - 1) / rows_cta, a.splits), warps * 32, smem, st>>>(a);
+  const int R = a.T * a.heads_per_group, rows_cta = row_warps * LAT_RW;
+  kern<<<dim3((R + rows_cta - 1) / rows_cta, a.splits, a.heads / a.heads_per_group), LAT_THREADS, smem, st>>>(a, row_warps);
   return 0;
 }
 
@@ -306,39 +329,40 @@ extern "C" int b2l_seq_latent_prep(const float* proj, int ld, int q_off, int q_r
   return 0;
 }
 
-extern "C" int b2l_seq_latent_attention_warps(int T, int heads) {
-  const int rows = T * heads;
+extern "C" int b2l_seq_latent_attention_warps(int T, int heads_per_group) {
+  const int rows = T * heads_per_group;
   int w = (rows + LAT_RW - 1) / LAT_RW;
   return w < 1 ? 1 : (w > 8 ? 8 : w);
 }
 
 extern "C" int b2l_seq_latent_attention(const b2l_seq_latent_attn_args* a, b2l_stream_t stream) {
   B2L_CHECK_ARG(a != nullptr, "b2l_seq_latent_attention: null args");
-  B2L_CHECK_ARG(a->q_lat && a->q_rot && a->cache && a->sink && a->meta && a->out, "b2l_seq_latent_attention: null pointer");
-  B2L_CHECK_ARG(a->T >= 0 && a->heads > 0 && a->rank > 0 && a->rot_dim >= 0 && a->max_pos > 0 && a->splits >= 1 && a->ldo >= a->heads * a->rank,
-                "b2l_seq_latent_attention: bad size");
+  B2L_CHECK_ARG(a->q_a && a->key_a && a->sink && a->meta && a->out && (a->n_b == 0 || (a->q_b && a->key_b)), "b2l_seq_latent_attention: null pointer");
+  B2L_CHECK_ARG(a->T >= 0 && a->heads > 0 && a->heads_per_group > 0 && a->heads % a->heads_per_group == 0 && a->n_a > 0 && a->n_b >= 0 &&
+                    a->vdim > 0 && a->vdim <= a->n_a && a->score_off >= 0 && a->score_off < a->n_a + a->n_b && a->score_off <= a->n_a &&
+                    a->splits >= 1 && a->ldo >= a->heads * a->vdim, "b2l_seq_latent_attention: bad size");
   B2L_CHECK_ARG(a->splits == 1 || a->work, "b2l_seq_latent_attention: key splits need a workspace");
-  B2L_CHECK_SUPPORTED(a->rank <= 512, "b2l_seq_latent_attention: latent size %d > 512", a->rank);
+  B2L_CHECK_SUPPORTED(a->vdim <= 512, "b2l_seq_latent_attention: value size %d > 512", a->vdim);
   if (a->T == 0) return 0;
-  const int warps = b2l_seq_latent_attention_warps(a->T, a->heads);
-  const int Kd = a->rank + a->rot_dim, Kp = (Kd + 3) & ~3;
-  const size_t smem = sizeof(float) * ((size_t)Kp * LAT_LDK + (size_t)warps * LAT_RW * Kp + (size_t)warps * LAT_RW * LAT_BN);
-  B2L_CHECK_SUPPORTED(smem <= 220 * 1024, "b2l_seq_latent_attention: key size %d needs %zu bytes of shared memory", Kd, smem);
+  const int row_warps = b2l_seq_latent_attention_warps(a->T, a->heads_per_group);
+  const int Kall = a->n_a + a->n_b, Kp = (Kall + 3) & ~3, Qp = Kp - (a->score_off & ~3);
+  const size_t smem = sizeof(float) * ((size_t)Kp * LAT_LDK + (size_t)row_warps * LAT_RW * Qp + (size_t)row_warps * LAT_RW * LAT_BN);
+  B2L_CHECK_SUPPORTED(smem <= 220 * 1024, "b2l_seq_latent_attention: key size %d needs %zu bytes of shared memory", Kall, smem);
   cudaStream_t st = (cudaStream_t)stream;
   int rc = 0;
   B2L_SEQ_DISPATCH(a->act_dtype, {
     const int base = sizeof(act_t) == 2 ? 0 : 4;
-    if (a->rank <= 64) rc = launch_latent<act_t, 2>(*a, warps, smem, base + 0, st);
-    else if (a->rank <= 128) rc = launch_latent<act_t, 4>(*a, warps, smem, base + 1, st);
-    else if (a->rank <= 256) rc = launch_latent<act_t, 8>(*a, warps, smem, base + 2, st);
-    else rc = launch_latent<act_t, 16>(*a, warps, smem, base + 3, st);
+    if (a->vdim <= 64) rc = launch_latent<act_t, 2>(*a, row_warps, smem, base + 0, st);
+    else if (a->vdim <= 128) rc = launch_latent<act_t, 4>(*a, row_warps, smem, base + 1, st);
+    else if (a->vdim <= 256) rc = launch_latent<act_t, 8>(*a, row_warps, smem, base + 2, st);
+    else rc = launch_latent<act_t, 16>(*a, row_warps, smem, base + 3, st);
   });
   if (rc != 0) return rc;
   B2L_LAUNCH_CHECK("seq_latent_attention_kernel");
   if (a->splits > 1) {
     const int R = a->T * a->heads;
     B2L_SEQ_DISPATCH(a->act_dtype, {
-      seq_latent_combine_kernel<act_t><<<(R + 3) / 4, 128, 0, st>>>(a->work, a->sink, (act_t*)a->out, a->ldo, R, a->heads, a->rank, a->splits);
+      seq_latent_combine_kernel<act_t><<<(R + 3) / 4, 128, 0, st>>>(a->work, a->sink, (act_t*)a->out, a->ldo, R, a->heads, a->vdim, a->splits);
     });
     B2L_LAUNCH_CHECK("seq_latent_combine_kernel");
   }

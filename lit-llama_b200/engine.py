@@ -79,7 +79,7 @@ class Engine:
         else:
             tok = torch.tensor(list(tokens), dtype=torch.int64).to(self.device)
             w = torch.tensor(want, dtype=torch.int32).to(self.device) if want else None
-            ctx = StepContext(T, self._meta, self.pool.tensors, self.model.dtype, pos_hint=pos0)
+            ctx = StepContext(T, self._meta, self.pool.tensors, self.model.dtype, pos_hint=pos0, slot_hint=slot)
             out = self.model.forward_portion(tok, ctx, w) if want else self._no_logits(tok, ctx)
         self.pool.advance(request_id, T)
         self.steps += 1

@@ -30,11 +30,12 @@ from .state import StateSpec
 
 class StepContext:
     """One portion of one sequence: T tokens, the device pair {slot, first position} and the slot pool's tensors.
-    `pos_hint` is the first position as the host knows it (None inside a captured step, which must not depend on it):
-    kernels never read it, it only sizes grids."""
+    `pos_hint` / `slot_hint` are the first position and the slot as the host knows them (None inside a captured step,
+    which must not depend on them): kernels never read them, they size grids and pick between equivalent forms."""
 
-    def __init__(self, T: int, meta: torch.Tensor, state: Dict[str, torch.Tensor], dtype: torch.dtype, pos_hint: Optional[int] = None) -> None:
-        self.T, self.meta, self.state, self.dtype, self.pos_hint = T, meta, state, dtype, pos_hint
+    def __init__(self, T: int, meta: torch.Tensor, state: Dict[str, torch.Tensor], dtype: torch.dtype, pos_hint: Optional[int] = None,
+                 slot_hint: Optional[int] = None) -> None:
+        self.T, self.meta, self.state, self.dtype, self.pos_hint, self.slot_hint = T, meta, state, dtype, pos_hint, slot_hint
         self.act = S.act_code(dtype)
 
     @property
@@ -364,10 +365,15 @@ class LatentAttention:
         key_h = [W_uk,h c | k_r],  value_h = W_uv,h c,  score = q . key * scale
         weights exp(s_j) / (exp(sink_h) + sum_j exp(s_j)),  y = W_o concat_h(sum_j weight_j value_j)
 
-    Only [c | k_r] is cached per position.  The attention runs in the latent space: the query is multiplied by W_uk
-    once (q' = W_uk,h^T q_h), scores are q' . c + q_r . k_r, the weighted sum of latents is mapped through W_uv
-    afterwards; every head reads the same cached row.  `rot`: {"base", "dims"} on the first `dims` entries of the
-    rotated part, pairs (2i, 2i+1) when `interleaved`."""
+    Only [c | k_r] is cached per position.  Single tokens and short portions attend in the latent space: the query is
+    multiplied by W_uk once (q' = W_uk,h^T q_h), scores are q' . c + q_r . k_r, the weighted sum of latents is mapped
+    through W_uv afterwards; every head reads the same cached row, once.  Portions of `expand_from` tokens or more
+    expand [value_h | key_h] of every cached position with one product and attend per head, which costs several times
+    fewer operations per (query, key) pair.  Both forms run the same kernel.  `rot`: {"base", "dims"} on the first
+    `dims` entries of the rotated part, pairs (2i, 2i+1) when `interleaved`."""
+
+    expand_from: int = 64                 # portions at least this long take the expanded form
+    expand_limit: int = 1 << 31           # ... unless the expansion would have more elements than this
 
     def __init__(self, name: str, W: Dict[str, torch.Tensor], p: str, *, heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int,
                  kv_rank: int, scale: float, eps: float, rot: Optional[dict], max_positions: int, interleaved: bool = True) -> None:
@@ -380,8 +386,10 @@ class LatentAttention:
         self.q_norm, self.kv_norm = W[p + "dq.norm"].contiguous(), W[p + "dkv.norm"].contiguous()
         self.w_uq = W[p + "uq"].contiguous()
         assert self.w_uq.shape == (heads * (dim + rot_dim), q_rank), "latent attention: query up-projection does not fit"
-        self.w_uk = W[p + "uk"].reshape(heads, dim, kv_rank).contiguous()                      # q' = q_h W_uk,h
-        self.w_uv_t = W[p + "uv"].reshape(heads, vdim, kv_rank).transpose(1, 2).contiguous()   # value = o' W_uv,h^T
+        uk, uv = W[p + "uk"].reshape(heads, dim, kv_rank), W[p + "uv"].reshape(heads, vdim, kv_rank)
+        self.w_uk = uk.contiguous()                                                            # q' = q_h W_uk,h
+        self.w_uv_t = uv.transpose(1, 2).contiguous()                                          # value = o' W_uv,h^T
+        self.w_expand = torch.cat([uv, uk], dim=1).reshape(heads * (vdim + dim), kv_rank).contiguous()   # per head [value | key] rows
         self.sink = W[p + "sink"].to(torch.float32).contiguous()
         self.w_o = W[p + "o"].contiguous()
         self.rot_dims, self.freq = 0, None
@@ -393,33 +401,55 @@ class LatentAttention:
     def state_specs(self) -> Dict[str, StateSpec]:
         return {self.name + ".kv": StateSpec((self.max_positions, self.rk + self.dr), self.w_o.dtype, zero_on_acquire=False)}
 
+    def _splits(self, ctx: StepContext, hpg: int) -> int:
+        """Key splits: fill the machine when there are few rows; never a function of the position inside a captured step."""
+        T = ctx.T
+        n_keys = self.max_positions if ctx.pos_hint is None else min(self.max_positions, ctx.pos_hint + T)
+        warps = S.lib().b2l_seq_latent_attention_warps(T, hpg)
+        ctas = -(-T * hpg // (4 * warps)) * (self.H // hpg)
+        return max(1, min(-(-296 // ctas), -(-n_keys // 64)))
+
+    def _attend(self, ctx: StepContext, out: torch.Tensor, vdim: int, splits: int, **kw) -> None:
+        work = torch.empty((splits, ctx.T * self.H, vdim + 2), dtype=torch.float32, device=out.device) if splits > 1 else None
+        a = S.LatentAttnArgs(sink=_p(self.sink), meta=_p(ctx.meta), out=_p(out), ldo=self.H * vdim, work=_p(work), scale=self.scale, T=ctx.T,
+                             heads=self.H, vdim=vdim, splits=splits, act_dtype=ctx.act, **kw)
+        S.check(S.lib().b2l_seq_latent_attention(C.byref(a), ctx.stream), "b2l_seq_latent_attention")
+
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         lib, T, dev, H = S.lib(), ctx.T, h.device, self.H
         proj = linear_f32(h, self.w_in)
         cq = torch.empty((T, self.rq), dtype=h.dtype, device=dev)
         cache = ctx.state[self.name + ".kv"]
+        Kd = self.rk + self.dr
         S.check(lib.b2l_seq_latent_prep(_p(proj), proj.shape[1], self.o_q, self.rq, _p(self.q_norm), _p(cq), self.o_kv, self.rk, _p(self.kv_norm),
                                         self.dr, _p(self.freq), self.rot_dims, int(self.interleaved), self.eps, _p(ctx.meta), _p(cache),
                                         self.max_positions, T, ctx.act, ctx.stream), "b2l_seq_latent_prep")
-        dq = self.dn + self.dr
+        dq, f32 = self.dn + self.dr, h.dtype == torch.float32
         q = linear(cq, self.w_uq)                                                   # [T, H * (dim + rot_dim)]
+        shared_b = dict(key_b=_p(cache, self.rk), ldkb=Kd, slot_stride_b=self.max_positions * Kd, n_b=self.dr)
+        n_pos = None if ctx.pos_hint is None or ctx.slot_hint is None else ctx.pos_hint + T
+        if n_pos is not None and T >= self.expand_from and n_pos * H * (self.dv + self.dn) <= self.expand_limit:
+            # expanded form: [value_h | key_h] of positions 0 .. n_pos-1 from the cached latents, one product
+            q32 = torch.empty((T, H * dq), dtype=torch.float32, device=dev)
+            S.check(lib.b2l_seq_rope(_p(q), H * dq, int(f32), _p(self.freq), self.rot_dims, int(self.interleaved), self.dn, 1.0, _p(ctx.meta),
+                                     _p(q32), H * dq, 1, T, H, dq, dq, dq, ctx.act, ctx.stream), "b2l_seq_rope")
+            kv = linear(cache[ctx.slot_hint, :n_pos, :self.rk], self.w_expand)       # [n_pos, H * (vdim + dim)]
+            att = torch.empty((T, H * self.dv), dtype=h.dtype, device=dev)
+            self._attend(ctx, att, self.dv, self._splits(ctx, 1), q_a=_p(q32), ldqa_t=H * dq, ldqa_h=dq, q_b=_p(q32, self.dn), ldqb_t=H * dq,
+                         ldqb_h=dq, key_a=_p(kv), ldka=H * (self.dv + self.dn), hska=self.dv + self.dn, slot_stride_a=0, n_a=self.dv + self.dn,
+                         score_off=self.dv, heads_per_group=1, **shared_b)
+            return linear(att, self.w_o)
+        # latent form
         qn = q.view(T, H, dq)[:, :, :self.dn].transpose(0, 1)                        # [H, T, dim]
-        q_lat = torch.bmm(qn, self.w_uk) if q.dtype == torch.float32 else torch.bmm(qn, self.w_uk, out_dtype=torch.float32)   # [H, T, rank] f32
+        q_lat = torch.bmm(qn, self.w_uk) if f32 else torch.bmm(qn, self.w_uk, out_dtype=torch.float32)     # [H, T, rank] f32
         q_rot = torch.empty((T, H, max(self.dr, 1)), dtype=torch.float32, device=dev)
         if self.dr:
-            S.check(lib.b2l_seq_rope(_p(q, self.dn), H * dq, int(q.dtype == torch.float32), _p(self.freq), self.rot_dims, int(self.interleaved), 0,
-                                     1.0, _p(ctx.meta), _p(q_rot), H * self.dr, 1, T, H, self.dr, dq, self.dr, ctx.act, ctx.stream), "b2l_seq_rope")
+            S.check(lib.b2l_seq_rope(_p(q, self.dn), H * dq, int(f32), _p(self.freq), self.rot_dims, int(self.interleaved), 0, 1.0, _p(ctx.meta),
+                                     _p(q_rot), H * self.dr, 1, T, H, self.dr, dq, self.dr, ctx.act, ctx.stream), "b2l_seq_rope")
         o_lat = torch.empty((T, H * self.rk), dtype=h.dtype, device=dev)
-        # key splits: fill the machine when there are few rows; never a function of the position inside a captured step
-        n_keys = self.max_positions if ctx.pos_hint is None else min(self.max_positions, ctx.pos_hint + T)
-        warps = lib.b2l_seq_latent_attention_warps(T, H)
-        row_blocks = -(-T * H // (4 * warps))
-        splits = max(1, min(-(-296 // row_blocks), -(-n_keys // 64)))
-        work = torch.empty((splits, T * H, self.rk + 2), dtype=torch.float32, device=dev) if splits > 1 else None
-        a = S.LatentAttnArgs(q_lat=_p(q_lat), ldq_t=self.rk, ldq_h=T * self.rk, q_rot=_p(q_rot), ldr=max(self.dr, 1), rot_off=0, cache=_p(cache),
-                             max_pos=self.max_positions, sink=_p(self.sink), meta=_p(ctx.meta), out=_p(o_lat), ldo=H * self.rk, work=_p(work),
-                             scale=self.scale, T=T, heads=H, rank=self.rk, rot_dim=self.dr, splits=splits, act_dtype=ctx.act)
-        S.check(lib.b2l_seq_latent_attention(C.byref(a), ctx.stream), "b2l_seq_latent_attention")
+        self._attend(ctx, o_lat, self.rk, self._splits(ctx, H), q_a=_p(q_lat), ldqa_t=self.rk, ldqa_h=T * self.rk, q_b=_p(q_rot),
+                     ldqb_t=H * max(self.dr, 1), ldqb_h=max(self.dr, 1), key_a=_p(cache), ldka=Kd, hska=0, slot_stride_a=self.max_positions * Kd,
+                     n_a=self.rk, score_off=0, heads_per_group=H, **shared_b)
         v = torch.bmm(o_lat.view(T, H, self.rk).transpose(0, 1), self.w_uv_t)        # [H, T, vdim]
         return linear(v.transpose(0, 1).reshape(T, H * self.dv), self.w_o)
 
@@ -486,6 +516,7 @@ class MoEFeedForward:
     sort the assignments by expert and run one pair of products per expert that received tokens."""
 
     SMALL = 4
+    grouped = True        # bf16, 16-byte rows: the library's grouped product instead of one product per expert
 
     def __init__(self, W: Dict[str, torch.Tensor], p: str, *, experts: int, identity: int, top: int, groups: int, keep: int, ff: int,
                  act: str = "silu") -> None:
@@ -541,18 +572,25 @@ class MoEFeedForward:
         meta = torch.empty((2 * (E + 1) + 2 * N,), dtype=torch.int32, device=dev)
         offsets, cursor, perm, inv = meta[:E + 1], meta[E + 1:2 * E + 2], meta[2 * E + 2:2 * E + 2 + N], meta[2 * E + 2 + N:]
         S.check(lib.b2l_seq_moe_sort(_p(idx), N, E, _p(offsets), _p(cursor), _p(perm), _p(inv), ctx.stream), "b2l_seq_moe_sort")
-        xg = torch.empty((N, D), dtype=h.dtype, device=dev)
+        xg = torch.empty((N + 8, D), dtype=h.dtype, device=dev)       # rows past the last group's end are never read
         S.check(lib.b2l_seq_moe_gather(_p(h), D, _p(perm), _p(offsets, E), top, _p(xg), N, D, ctx.act, ctx.stream), "b2l_seq_moe_gather")
-        off = offsets.cpu().tolist()                                   # the one host read of a long portion
         gu = torch.empty((N, 2 * ff), dtype=h.dtype, device=dev)
-        for e in range(E):
-            if off[e + 1] > off[e]:
-                torch.mm(xg[off[e]:off[e + 1]], self.w_gu[e].t(), out=gu[off[e]:off[e + 1]])
-        mid = torch.empty((N, ff), dtype=h.dtype, device=dev)
-        S.check(lib.b2l_seq_gated_act(_p(gu), 2 * ff, _p(mid), off[E], ff, self.act, ctx.act, ctx.stream), "b2l_seq_gated_act")
-        yg = torch.empty((N, D), dtype=h.dtype, device=dev)
-        for e in range(E):
-            if off[e + 1] > off[e]:
-                torch.mm(mid[off[e]:off[e + 1]], self.w_down[e].t(), out=yg[off[e]:off[e + 1]])
+        mid = torch.empty((N + 8, ff), dtype=h.dtype, device=dev)
+        if self.grouped and h.dtype == torch.bfloat16 and D % 8 == 0 and ff % 8 == 0:
+            # the library's grouped product: every expert's rows in one launch, group ends read on the device
+            ends = offsets[1:]
+            gu = F.grouped_mm(xg, self.w_gu.transpose(1, 2), offs=ends)
+            S.check(lib.b2l_seq_gated_act(_p(gu), 2 * ff, _p(mid), N, ff, self.act, ctx.act, ctx.stream), "b2l_seq_gated_act")
+            yg = F.grouped_mm(mid, self.w_down.transpose(1, 2), offs=ends)
+        else:
+            off = offsets.cpu().tolist()                               # the one host read of a long portion
+            for e in range(E):
+                if off[e + 1] > off[e]:
+                    torch.mm(xg[off[e]:off[e + 1]], self.w_gu[e].t(), out=gu[off[e]:off[e + 1]])
+            S.check(lib.b2l_seq_gated_act(_p(gu), 2 * ff, _p(mid), off[E], ff, self.act, ctx.act, ctx.stream), "b2l_seq_gated_act")
+            yg = torch.empty((N, D), dtype=h.dtype, device=dev)
+            for e in range(E):
+                if off[e + 1] > off[e]:
+                    torch.mm(mid[off[e]:off[e + 1]], self.w_down[e].t(), out=yg[off[e]:off[e + 1]])
         S.check(lib.b2l_seq_moe_combine(_p(yg), _p(inv), _p(wgt), _p(h), D, _p(y), D, T, D, top, ctx.act, ctx.stream), "b2l_seq_moe_combine")
         return y

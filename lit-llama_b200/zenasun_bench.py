@@ -81,11 +81,11 @@ def kernel_table(model, engine, T: int, device, timer, peaks: dict) -> List[dict
                      "GFLOP_s": flops / t / 1e9, "note": note})
 
     # fill the cache of the slot once, so that a single token at position T has T keys to read
-    full = M.StepContext(T, torch.tensor([slot, 0], dtype=torch.int32, device=device), engine.pool.tensors, dt, pos_hint=0)
+    full = M.StepContext(T, torch.tensor([slot, 0], dtype=torch.int32, device=device), engine.pool.tensors, dt, pos_hint=0, slot_hint=slot)
     att.forward(torch.randn(T, D, device=device).to(dt), full)
     for tt, pos0 in ((T, 0), (1, T)):
         meta = torch.tensor([slot, pos0], dtype=torch.int32, device=device)
-        ctx = M.StepContext(tt, meta, engine.pool.tensors, dt, pos_hint=pos0 if tt > 1 else None)
+        ctx = M.StepContext(tt, meta, engine.pool.tensors, dt, pos_hint=pos0 if tt > 1 else None, slot_hint=slot if tt > 1 else None)
         hh = torch.randn(tt, D, device=device).to(dt)
         x = torch.randn(tt, D, device=device)
         y1, y2 = torch.randn(tt, D, device=device).to(dt), torch.randn(tt, D, device=device).to(dt)
@@ -94,25 +94,37 @@ def kernel_table(model, engine, T: int, device, timer, peaks: dict) -> List[dict
         t = timer(lambda: S.check(lib.b2l_seq_add_norm2(M._p(y1), M._p(y2), M._p(x), M._p(w), M._p(h1), M._p(w), M._p(h2), 1.0, 1e-6, None, tt, D,
                                                         ctx.act, ctx.stream), "k"))
         add("seq_add_norm2_kernel", "seq_norm_add_norm_kernel", tt, t, tt * D * (2 * es + 4 + 4 + 2 * es))
-        # the attention kernel alone on prepared queries
-        H, rk, dr = att.H, att.rk, att.dr
-        q_lat = torch.randn(H, tt, rk, device=device)
-        q_rot = torch.randn(tt, H, dr, device=device)
-        o_lat = torch.empty(tt, H * rk, dtype=dt, device=device)
+        # the attention kernel alone, in the form the mixer picks for this portion (its own products excluded)
+        H, rk, dr, dn, dv = att.H, att.rk, att.dr, att.dn, att.dv
         n_keys = pos0 + tt
-        warps = lib.b2l_seq_latent_attention_warps(tt, H)
-        row_blocks = -(-tt * H // (4 * warps))
-        splits = max(1, min(-(-296 // row_blocks), -(-(n_keys if tt > 1 else att.max_positions) // 64)))
-        work = torch.empty((splits, tt * H, rk + 2), dtype=torch.float32, device=device)
-        a = S.LatentAttnArgs(q_lat=M._p(q_lat), ldq_t=rk, ldq_h=tt * rk, q_rot=M._p(q_rot), ldr=dr, rot_off=0, cache=M._p(ctx.state[att.name + ".kv"]),
-                             max_pos=att.max_positions, sink=M._p(att.sink), meta=M._p(meta), out=M._p(o_lat), ldo=H * rk, work=M._p(work),
-                             scale=att.scale, T=tt, heads=H, rank=rk, rot_dim=dr, splits=splits, act_dtype=ctx.act)
-        t = timer(lambda: S.check(lib.b2l_seq_latent_attention(C.byref(a), ctx.stream), "k"))
+        expanded = tt >= att.expand_from
         keys = (tt + 1) / 2 if tt > 1 else n_keys
-        fl = 2.0 * tt * H * keys * (2 * rk + dr)
-        nb = n_keys * (rk + dr) * es + tt * H * ((rk + dr) * 4 + rk * es)
-        add("seq_latent_attention_kernel", "seq_block_attention_tile_kernel" if tt > 1 else "seq_block_attention_kernel", tt, t, nb, fl,
-            f"f32 scores on CUDA cores, latent space, {splits} key split(s)")
+        Kd = rk + dr
+        shared_b = dict(key_b=M._p(ctx.state[att.name + ".kv"], rk), ldkb=Kd, slot_stride_b=att.max_positions * Kd, n_b=dr)
+        if expanded:
+            q32 = torch.randn(tt, H * (dn + dr), device=device)
+            kv = torch.randn(n_keys, H * (dv + dn), device=device).to(dt)
+            out_a = torch.empty(tt, H * dv, dtype=dt, device=device)
+            ctx.slot_hint = slot
+            splits = att._splits(ctx, 1)
+            t = timer(lambda: att._attend(ctx, out_a, dv, splits, q_a=M._p(q32), ldqa_t=H * (dn + dr), ldqa_h=dn + dr, q_b=M._p(q32, dn),
+                                          ldqb_t=H * (dn + dr), ldqb_h=dn + dr, key_a=M._p(kv), ldka=H * (dv + dn), hska=dv + dn, slot_stride_a=0,
+                                          n_a=dv + dn, score_off=dv, heads_per_group=1, **shared_b))
+            fl = 2.0 * tt * H * keys * (dn + dr + dv)
+            nb = n_keys * (H * (dv + dn) + dr) * es + tt * H * ((dn + dr) * 4 + dv * es)
+        else:
+            q_lat = torch.randn(H, tt, rk, device=device)
+            q_rot = torch.randn(tt, H, dr, device=device)
+            out_a = torch.empty(tt, H * rk, dtype=dt, device=device)
+            splits = att._splits(ctx, H)
+            t = timer(lambda: att._attend(ctx, out_a, rk, splits, q_a=M._p(q_lat), ldqa_t=rk, ldqa_h=tt * rk, q_b=M._p(q_rot), ldqb_t=H * dr, ldqb_h=dr,
+                                          key_a=M._p(ctx.state[att.name + ".kv"]), ldka=Kd, hska=0, slot_stride_a=att.max_positions * Kd, n_a=rk,
+                                          score_off=0, heads_per_group=H, **shared_b))
+            fl = 2.0 * tt * H * keys * (2 * rk + dr)
+            nb = n_keys * Kd * es + tt * H * (Kd * 4 + rk * es)
+        add("seq_latent_attention_kernel (" + ("expanded" if expanded else "latent") + " form)",
+            "seq_block_attention_tile_kernel" if tt > 1 else "seq_block_attention_kernel", tt, t, nb, fl,
+            f"f32 scores on CUDA cores, {splits} key split(s)")
         t = timer(lambda: att.forward(hh, ctx))
         wb = (att.w_in.numel() + att.w_uq.numel() + att.w_uk.numel() + att.w_uv_t.numel() + att.w_o.numel()) * es
         add("LatentAttention whole (5 products + prep + rotation + attention)", "attention branch", tt, t, wb + nb, fl + 2.0 * tt * wb / es)

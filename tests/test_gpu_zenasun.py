@@ -266,7 +266,7 @@ def test_registry_loads_a_saved_model(tmp_path):
 def _ctx(M, P, mixer, T, pos0, dtype, slot=0, pool=None, hint=True):
     pool = pool or P.SequenceStatePool(mixer.state_specs(), 2, torch.device(DEV))
     meta = torch.tensor([slot, pos0], dtype=torch.int32, device=DEV)
-    return M.StepContext(T, meta, pool.tensors, dtype, pos_hint=pos0 if hint else None), pool, meta
+    return M.StepContext(T, meta, pool.tensors, dtype, pos_hint=pos0 if hint else None, slot_hint=slot if hint else None), pool, meta
 
 
 @pytest.mark.parametrize("sizes", [(3, 20, 12, 28, 40, 36), (1, 8, 2, 4, 8, 70), (6, 16, 16, 16, 32, 150), (2, 4, 6, 300, 12, 260)])
@@ -282,9 +282,12 @@ def test_latent_attention_alone(sizes):
     mixer = M.LatentAttention("x", {k: v.to(DEV) for k, v in W.items()}, "mix.", heads=H, dim=dn, rot_dim=dr, vdim=dv, q_rank=rq, kv_rank=rk,
                               scale=0.2, eps=eps, rot=m["rot"], max_positions=128)
     ctx, pool, meta = _ctx(M, P, mixer, T, 0, torch.float32, slot=1)
-    got = mixer.forward(h.to(DEV), ctx)
+    got = mixer.forward(h.to(DEV), ctx)                                   # a long portion: expanded keys and values per head
     assert rel(got, want) < 2e-5
-    # the same in three portions on the other slot, the last one without the host's position (fixed grid)
+    mixer.expand_from = 10 ** 9
+    assert rel(mixer.forward(h.to(DEV), ctx), want) < 2e-5                # the same portion in the latent space
+    mixer.expand_from = 40
+    # the same in three portions on the other slot (latent, expanded over older positions, latent on a fixed grid)
     outs, at = [], 0
     for n, hint in ((31, True), (43, True), (1, False)):
         ctx, pool, meta = _ctx(M, P, mixer, n, at, torch.float32, slot=0, pool=pool, hint=hint)
@@ -294,16 +297,19 @@ def test_latent_attention_alone(sizes):
 
 
 def _latent_kernel(S, cache, q_lat, q_rot, sink, scale, pos0, splits, slot=0):
-    """The attention kernel on a cache filled by the test: q_lat [T, H, rank], q_rot [T, H, rot]; returns [T, H, rank]."""
+    """The attention kernel in its latent form on a cache filled by the test: q_lat [T, H, rank], q_rot [T, H, rot];
+    returns [T, H, rank]."""
     T, H, rank = q_lat.shape
     rot = q_rot.shape[2]
     out = torch.empty(T, H * rank, device=DEV)
     work = torch.empty(max(splits, 1), T * H, rank + 2, device=DEV)
     meta = torch.tensor([slot, pos0], dtype=torch.int32, device=DEV)
     ql, qr = q_lat.to(DEV).contiguous(), q_rot.to(DEV).contiguous()
-    a = S.LatentAttnArgs(q_lat=ql.data_ptr(), ldq_t=H * rank, ldq_h=rank, q_rot=qr.data_ptr(), ldr=rot, rot_off=0, cache=cache.data_ptr(),
-                         max_pos=cache.shape[1], sink=sink.data_ptr(), meta=meta.data_ptr(), out=out.data_ptr(), ldo=H * rank, work=work.data_ptr(),
-                         scale=scale, T=T, heads=H, rank=rank, rot_dim=rot, splits=splits, act_dtype=S.B2L_F32)
+    Kd = rank + rot
+    a = S.LatentAttnArgs(q_a=ql.data_ptr(), ldqa_t=H * rank, ldqa_h=rank, q_b=qr.data_ptr(), ldqb_t=H * rot, ldqb_h=rot, key_a=cache.data_ptr(), ldka=Kd,
+                         hska=0, slot_stride_a=cache.shape[1] * Kd, key_b=cache.data_ptr() + 4 * rank, ldkb=Kd, slot_stride_b=cache.shape[1] * Kd,
+                         sink=sink.data_ptr(), meta=meta.data_ptr(), out=out.data_ptr(), ldo=H * rank, work=work.data_ptr(), scale=scale, T=T, heads=H,
+                         heads_per_group=H, n_a=rank, n_b=rot, vdim=rank, score_off=0, splits=splits, act_dtype=S.B2L_F32)
     S.check(S.lib().b2l_seq_latent_attention(C.byref(a), torch.cuda.current_stream().cuda_stream), "b2l_seq_latent_attention")
     torch.cuda.synchronize()
     return out.view(T, H, rank).cpu()
@@ -329,8 +335,7 @@ def test_latent_attention_far_keys_and_the_causal_edge(splits):
     P, S, M = _pkg()
     rank, rot, H, n = 20, 6, 3, 400
     g = torch.Generator().manual_seed(9)
-    cache = torch.randn(2, 512, rank + rot, generator=g)
-    cache_d = cache.to(DEV)
+    base = torch.randn(2, 512, rank + rot, generator=g)
     sink = torch.tensor([-30.0, 0.0, 2.0])
     sink_d = sink.to(DEV)
     pos0 = n - 2                               # two queries at positions n-2 and n-1

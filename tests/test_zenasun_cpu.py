@@ -49,13 +49,13 @@ def test_latent_argument_block_matches_the_header(tmp_path):
 
     prog = tmp_path / "layout.c"
     prog.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "b2l_seq.h"\nint main(void){printf("%zu %zu %zu %zu %zu\\n", '
-                    "sizeof(b2l_seq_latent_attn_args), offsetof(b2l_seq_latent_attn_args, q_rot), offsetof(b2l_seq_latent_attn_args, sink), "
+                    "sizeof(b2l_seq_latent_attn_args), offsetof(b2l_seq_latent_attn_args, key_b), offsetof(b2l_seq_latent_attn_args, sink), "
                     "offsetof(b2l_seq_latent_attn_args, scale), offsetof(b2l_seq_latent_attn_args, act_dtype));return 0;}\n")
     exe = tmp_path / "layout"
     subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(prog), "-o", str(exe)], check=True)
     out = [int(v) for v in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
     A = S.LatentAttnArgs
-    assert out == [C.sizeof(A), A.q_rot.offset, A.sink.offset, A.scale.offset, A.act_dtype.offset]
+    assert out == [C.sizeof(A), A.key_b.offset, A.sink.offset, A.scale.offset, A.act_dtype.offset]
 
 
 def test_oracle_retention_state_carries():
