@@ -243,29 +243,43 @@ __global__ void __launch_bounds__(LAT_THREADS) seq_latent_attention_kernel(b2l_s
   }
 }
 
-// Merges the key splits of a row and adds the sink.  One warp per row (t, h).
+// Merges the key splits of a row and adds the sink.  One CTA per row (t, h): warp 0 turns every split's running
+// maximum and sum into one factor exp(m_s - M) / denominator, then the threads own value entries and add the
+// splits' accumulators with independent loads.
 template <typename act_t>
-__global__ void seq_latent_combine_kernel(const float* __restrict__ work, const float* __restrict__ sink, act_t* __restrict__ out, int ldo,
-                                          int R, int heads, int vdim, int splits) {
-  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (row >= R) return;
-  const int t = row / heads, h = row % heads;
+__global__ void __launch_bounds__(128) seq_latent_combine_kernel(const float* __restrict__ work, const float* __restrict__ sink,
+                                                                 act_t* __restrict__ out, int ldo, int R, int heads, int vdim, int splits) {
+  extern __shared__ float comb_f[];                      // [splits]
+  const int row = blockIdx.x, t = row / heads, h = row % heads;
   const size_t stride = (size_t)(vdim + 2);
-  float M = sink[h];
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, work[((size_t)s * R + row) * stride]);
-  float den = expf(sink[h] - M);
-  for (int s = 0; s < splits; ++s) {
-    const float* w = work + ((size_t)s * R + row) * stride;
-    if (w[0] > -INFINITY) den += w[1] * expf(w[0] - M);
-  }
-  act_t* o = out + (size_t)t * ldo + (size_t)h * vdim;
-  for (int v = lane; v < vdim; v += 32) {
-    float acc = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float* w = work + ((size_t)s * R + row) * stride;
-      if (w[0] > -INFINITY) acc += w[2 + v] * expf(w[0] - M);
+  const float* w0 = work + (size_t)row * stride;
+  const size_t sstep = (size_t)R * stride;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    const float sk = sink[h];
+    float M = sk;
+    for (int s = lane; s < splits; s += 32) M = fmaxf(M, w0[(size_t)s * sstep]);
+    M = warp_max(M);
+    float den = 0.f;
+    for (int s = lane; s < splits; s += 32) {
+      const float m = w0[(size_t)s * sstep];
+      const float f = m > -INFINITY ? expf(m - M) : 0.f;
+      comb_f[s] = f;
+      den += f * w0[(size_t)s * sstep + 1];
     }
-    st_act(o, v, acc / den);
+    den = warp_sum(den) + expf(sk - M);
+    const float inv = 1.0f / den;
+    for (int s = lane; s < splits; s += 32) comb_f[s] *= inv;
+  }
+  __syncthreads();
+  act_t* o = out + (size_t)t * ldo + (size_t)h * vdim;
+  for (int v = threadIdx.x; v < vdim; v += blockDim.x) {
+    float acc = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < splits; ++s) {
+      acc = fmaf(w0[(size_t)s * sstep + 2 + v], comb_f[s], acc);            // an empty split wrote zeros and has factor 0
+    }
+    st_act(o, v, acc);
   }
 }
 
@@ -342,6 +356,7 @@ extern "C" int b2l_seq_latent_attention(const b2l_seq_latent_attn_args* a, b2l_s
                     a->vdim > 0 && a->vdim <= a->n_a && a->score_off >= 0 && a->score_off < a->n_a + a->n_b && a->score_off <= a->n_a &&
                     a->splits >= 1 && a->ldo >= a->heads * a->vdim, "b2l_seq_latent_attention: bad size");
   B2L_CHECK_ARG(a->splits == 1 || a->work, "b2l_seq_latent_attention: key splits need a workspace");
+  B2L_CHECK_SUPPORTED(a->splits <= 4096, "b2l_seq_latent_attention: %d key splits > 4096", a->splits);
   B2L_CHECK_SUPPORTED(a->vdim <= 512, "b2l_seq_latent_attention: value size %d > 512", a->vdim);
   if (a->T == 0) return 0;
   const int row_warps = b2l_seq_latent_attention_warps(a->T, a->heads_per_group);
@@ -362,7 +377,7 @@ extern "C" int b2l_seq_latent_attention(const b2l_seq_latent_attn_args* a, b2l_s
   if (a->splits > 1) {
     const int R = a->T * a->heads;
     B2L_SEQ_DISPATCH(a->act_dtype, {
-      seq_latent_combine_kernel<act_t><<<(R + 3) / 4, 128, 0, st>>>(a->work, a->sink, (act_t*)a->out, a->ldo, R, a->heads, a->vdim, a->splits);
+      seq_latent_combine_kernel<act_t><<<R, 128, sizeof(float) * a->splits, st>>>(a->work, a->sink, (act_t*)a->out, a->ldo, R, a->heads, a->vdim, a->splits);
     });
     B2L_LAUNCH_CHECK("seq_latent_combine_kernel");
   }

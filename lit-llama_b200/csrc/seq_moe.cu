@@ -273,9 +273,9 @@ extern "C" int b2l_seq_moe_experts_small(const void* h, int ldh, const void* w_g
     rc = ensure_dyn_smem(seq_moe_down_kernel<act_t>, smem_dn, g_moe_smem[sizeof(act_t) == 2 ? 2 : 3]);
     if (rc != 0) return rc;
     if (n_real > 0)
-      seq_moe_up_kernel<act_t><<<dim3(T * top, (ff + 63) / 64), 256, smem_up, st>>>((const act_t*)h, ldh, (const act_t*)w_gate_up, idx, (act_t*)mid,
+      seq_moe_up_kernel<act_t><<<dim3(T * top, (ff + 7) / 8), 256, smem_up, st>>>((const act_t*)h, ldh, (const act_t*)w_gate_up, idx, (act_t*)mid,
                                                                                    D, ff, n_real, top, vec_up);
-    seq_moe_down_kernel<act_t><<<dim3(T, (D + 63) / 64), 256, smem_dn, st>>>((const act_t*)mid, (const act_t*)w_down, idx, weights, (const act_t*)h,
+    seq_moe_down_kernel<act_t><<<dim3(T, (D + 7) / 8), 256, smem_dn, st>>>((const act_t*)mid, (const act_t*)w_down, idx, weights, (const act_t*)h,
                                                                             ldh, (act_t*)y, ldy, D, ff, n_real, top, vec_dn);
   });
   B2L_LAUNCH_CHECK("seq_moe_up_kernel / seq_moe_down_kernel");

@@ -342,7 +342,10 @@ def test_latent_attention_far_keys_and_the_causal_edge(splits):
     for target in (0, 1, 31, 32, 33, 63, 64, 133, 134, 255, 256, n - 3, n - 2, n - 1):
         q_lat = 0.05 * torch.randn(2, H, rank, generator=g)
         q_rot = 0.05 * torch.randn(2, H, rot, generator=g)
-        q_lat[:, 0] += 12.0 * cache[1, target, :rank] / cache[1, target, :rank].norm() * math.sqrt(rank)              # head 0 of both queries looks for `target` in slot 1
+        cache = base.clone()
+        cache[1, target, :rank] *= 3.0                               # a long key, and a query along it: its score stands out by > 30
+        q_lat[:, 0] += 4.0 * cache[1, target, :rank] / cache[1, target, :rank].norm()
+        cache_d = cache.to(DEV)
         got = _latent_kernel(S, cache_d, q_lat, q_rot, sink_d, 1.0, pos0, splits, slot=1)
         want = _latent_plain(cache[1], q_lat, q_rot, sink, 1.0, pos0)
         assert rel(got, want) < 2e-5, (target, rel(got, want))
