@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(LAT_THREADS) seq_latent_attention_kernel(b2l_s
 // maximum and sum into one factor exp(m_s - M) / denominator, then the threads own value entries and add the
 // splits' accumulators with independent loads.
 template <typename act_t>
-__global__ void __launch_bounds__(128) seq_latent_combine_kernel(const float* __restrict__ work, const float* __restrict__ sink,
+__global__ void __launch_bounds__(256) seq_latent_combine_kernel(const float* __restrict__ work, const float* __restrict__ sink,
                                                                  act_t* __restrict__ out, int ldo, int R, int heads, int vdim, int splits) {
   extern __shared__ float comb_f[];                      // [splits]
   const int row = blockIdx.x, t = row / heads, h = row % heads;
@@ -275,7 +275,7 @@ __global__ void __launch_bounds__(128) seq_latent_combine_kernel(const float* __
   act_t* o = out + (size_t)t * ldo + (size_t)h * vdim;
   for (int v = threadIdx.x; v < vdim; v += blockDim.x) {
     float acc = 0.f;
-#pragma unroll 8
+#pragma unroll 16
     for (int s = 0; s < splits; ++s) {
       acc = fmaf(w0[(size_t)s * sstep + 2 + v], comb_f[s], acc);            // an empty split wrote zeros and has factor 0
     }
@@ -377,7 +377,7 @@ extern "C" int b2l_seq_latent_attention(const b2l_seq_latent_attn_args* a, b2l_s
   if (a->splits > 1) {
     const int R = a->T * a->heads;
     B2L_SEQ_DISPATCH(a->act_dtype, {
-      seq_latent_combine_kernel<act_t><<<R, 128, sizeof(float) * a->splits, st>>>(a->work, a->sink, (act_t*)a->out, a->ldo, R, a->heads, a->vdim, a->splits);
+      seq_latent_combine_kernel<act_t><<<R, a->vdim > 128 ? 256 : 128, sizeof(float) * a->splits, st>>>(a->work, a->sink, (act_t*)a->out, a->ldo, R, a->heads, a->vdim, a->splits);
     });
     B2L_LAUNCH_CHECK("seq_latent_combine_kernel");
   }

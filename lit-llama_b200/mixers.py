@@ -407,7 +407,7 @@ class LatentAttention:
         n_keys = self.max_positions if ctx.pos_hint is None else min(self.max_positions, ctx.pos_hint + T)
         warps = S.lib().b2l_seq_latent_attention_warps(T, hpg)
         ctas = -(-T * hpg // (4 * warps)) * (self.H // hpg)
-        return max(1, min(-(-296 // ctas), -(-n_keys // 64)))
+        return max(1, min(-(-296 // ctas), -(-n_keys // 32)))
 
     def _attend(self, ctx: StepContext, out: torch.Tensor, vdim: int, splits: int, **kw) -> None:
         work = torch.empty((splits, ctx.T * self.H, vdim + 2), dtype=torch.float32, device=out.device) if splits > 1 else None
@@ -527,7 +527,7 @@ class MoEFeedForward:
         self.act = GatedMLP.ACTS[act]
         if self.act != S.ACT_SILU:
             raise ValueError("routed experts: the device-indexed products implement silu only")
-        self.w_router = W[p + "router"].to(torch.float32).contiguous()
+        self.w_router = W[p + "router"].contiguous()
         assert self.w_router.shape[0] == self.n, "routed experts: the router does not have experts + identity outputs"
         self.correction = W[p + "correction"].to(torch.float32).contiguous() if (p + "correction") in W else None
         dev, dt = self.w_router.device, W[p + "router"].dtype
@@ -546,12 +546,8 @@ class MoEFeedForward:
         lib, T, dev, D = S.lib(), ctx.T, h.device, h.shape[1]
         if torch.backends.cuda.matmul.allow_tf32:
             raise RuntimeError("router logits need true 32-bit products: torch.backends.cuda.matmul.allow_tf32 is on")
-        if h.dtype == torch.float32:
-            h32 = h
-        else:
-            h32 = torch.empty((T, D), dtype=torch.float32, device=dev)
-            S.check(lib.b2l_seq_cast_f32(_p(h), D, _p(h32), D, T, D, ctx.act, ctx.stream), "b2l_seq_cast_f32")
-        z = F.linear(h32, self.w_router)
+        # f32 logits: bf16 activations and router weights are exact in f32, the product keeps its f32 accumulator
+        z = linear_f32(h, self.w_router)
         idx = torch.empty((T, self.top), dtype=torch.int32, device=dev)
         wgt = torch.empty((T, self.top), dtype=torch.float32, device=dev)
         S.check(lib.b2l_seq_moe_route(_p(z), self.n, _p(self.correction), self.n, self.groups, self.keep, self.top, _p(idx), _p(wgt), T,
