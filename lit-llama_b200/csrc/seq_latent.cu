@@ -99,7 +99,7 @@ constexpr int LAT_THREADS = 256;
 // tile (q read as broadcast float4, kT conflict-free).  Values: lane owns value entries lane + 32 i (weights read
 // as broadcast float4, kT with stride 33 conflict-free).
 template <typename act_t, int VI>
-__global__ void __launch_bounds__(LAT_THREADS) seq_latent_attention_kernel(b2l_seq_latent_attn_args a, int row_warps) {
+__global__ void __launch_bounds__(LAT_THREADS, VI <= 4 ? 3 : 1) seq_latent_attention_kernel(b2l_seq_latent_attn_args a, int row_warps) {
   extern __shared__ __align__(16) float lat_smem[];
   const int Kall = a.n_a + a.n_b, Kp = (Kall + 3) & ~3;
   const int s0 = a.score_off & ~3, Qp = Kp - s0;                       // scores run over d in [s0, Kp), q is zero below score_off
@@ -165,6 +165,7 @@ __global__ void __launch_bounds__(LAT_THREADS) seq_latent_attention_kernel(b2l_s
     __syncthreads();
     if (jt > warp_lim) continue;                                    // every key of the tile lies after this warp's rows
     float s[LAT_RW] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
     for (int d = s0; d < Kp; d += 4) {
       const float k0 = kT[(size_t)d * LAT_LDK + lane], k1 = kT[(size_t)(d + 1) * LAT_LDK + lane];
       const float k2 = kT[(size_t)(d + 2) * LAT_LDK + lane], k3 = kT[(size_t)(d + 3) * LAT_LDK + lane];
@@ -192,6 +193,7 @@ __global__ void __launch_bounds__(LAT_THREADS) seq_latent_attention_kernel(b2l_s
       pw[r * LAT_BN + lane] = p;
     }
     __syncwarp();
+#pragma unroll 2
     for (int jj = 0; jj < LAT_BN; jj += 4) {
       float4 p4[LAT_RW];
 #pragma unroll

@@ -407,6 +407,8 @@ class LatentAttention:
         n_keys = self.max_positions if ctx.pos_hint is None else min(self.max_positions, ctx.pos_hint + T)
         warps = S.lib().b2l_seq_latent_attention_warps(T, hpg)
         ctas = -(-T * hpg // (4 * warps)) * (self.H // hpg)
+        if ctas >= 148:
+            return 1
         return max(1, min(-(-296 // ctas), -(-n_keys // 32)))
 
     def _attend(self, ctx: StepContext, out: torch.Tensor, vdim: int, splits: int, **kw) -> None:
