@@ -256,6 +256,17 @@ def test_greedy_generation_through_the_scheduler():
     assert engine.generate(prompts[0], 4)[:len(prompts[0])] == prompts[0]
 
 
+def test_sampled_generation_runs_and_respects_eos():
+    cfg = cfg_b()
+    model, engine, W = build(cfg, torch.bfloat16)
+    torch.manual_seed(0)
+    prompt = tokens_of(cfg, 9)
+    out = engine.generate(prompt, 12, temperature=0.8, top_k=5)
+    assert len(out) == 21 and all(0 <= t < cfg["vocab"] for t in out)
+    first = engine.generate(prompt, 4)[9]
+    assert engine.generate(prompt, 12, eos_id=first) == prompt + [first]
+
+
 def test_registry_loads_a_saved_model(tmp_path):
     P, S, M = _pkg()
     from lit_llama_b200.checkpoint_io import write_safetensors
