@@ -201,6 +201,11 @@ int b2l_seq_latent_attention_warps(int T, int heads_per_group);    /* warps per 
 int b2l_seq_moe_route(const float* logits, int ld, const float* correction, int n, int groups, int keep, int top, int* idx,
                       float* weights, int T, b2l_stream_t stream);
 
+/* The same with the logits computed in the kernel, for a few tokens: logits[t] = w_router h[t] (w_router act [n][D],
+ * f32 accumulation), one CTA per token, one launch for product and routing. */
+int b2l_seq_moe_route_fused(const void* h, int ldh, const void* w_router, const float* correction, int D, int n, int groups, int keep,
+                            int top, int* idx, float* weights, int T, int act_dtype, b2l_stream_t stream);
+
 /* Experts of a few tokens, indices read on the device.  Expert e < n_real: W_down[e] (silu(W_gate[e] h) * (W_up[e] h))
  * with w_gate_up act [n_real][2*ff][D] (gate rows, then up rows) and w_down act [n_real][D][ff]; e >= n_real: h itself.
  * y[t] = sum_k weights[t, k] * expert_idx[t,k](h[t]).  mid: act [T*top, ff] scratch. */

@@ -93,6 +93,8 @@ _SIGS = {
     "b2l_seq_latent_attention": (c_int, [C.POINTER(LatentAttnArgs), c_void_p]),
     "b2l_seq_latent_attention_warps": (c_int, [c_int, c_int]),
     "b2l_seq_moe_route": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "b2l_seq_moe_route_fused": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                                        c_void_p]),
     "b2l_seq_moe_experts_small": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                           c_int, c_int, c_int, c_int, c_void_p]),
     "b2l_seq_moe_sort": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -25,17 +25,10 @@ __device__ __forceinline__ Best warp_best(Best x) {
   return x;
 }
 
-// One warp per token.  Shared per warp: s[n] (scores), c[n] (choice scores), g[groups].
-__global__ void seq_moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ corr, int n, int groups, int keep,
-                                     int top, int* __restrict__ idx, float* __restrict__ wgt, int T) {
-  extern __shared__ float route_smem[];
-  const int wpc = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * wpc + warp;
-  if (t >= T) return;
-  float* s = route_smem + (size_t)warp * (2 * n + groups);
-  float* c = s + n;
-  float* g = c + n;
-  const float* zr = z + (size_t)t * ldz;
+// The router of one token by one warp, from its logits zr[n] (global or shared).  s[n] (scores), c[n] (choice
+// scores) and g[groups] are the warp's shared scratch.
+__device__ __forceinline__ void route_token(const float* zr, const float* __restrict__ corr, int n, int groups, int keep, int top,
+                                            int* __restrict__ idx_t, float* __restrict__ wgt_t, float* s, float* c, float* g, int lane) {
   float mx = -INFINITY;
   for (int i = lane; i < n; i += 32) mx = fmaxf(mx, zr[i]);
   mx = warp_max(mx);
@@ -79,13 +72,24 @@ __global__ void seq_moe_route_kernel(const float* __restrict__ z, int ldz, const
     b = warp_best(b);
     const int e = b.i == INT_MAX ? 0 : b.i;
     if (lane == 0) {
-      idx[(size_t)t * top + k] = e;
+      idx_t[k] = e;
       c[e] = NAN;                                   // chosen: out of the next rounds
     }
     total += s[e];
     __syncwarp();
   }
-  for (int k = lane; k < top; k += 32) wgt[(size_t)t * top + k] = s[idx[(size_t)t * top + k]] / (total + 1e-20f);
+  for (int k = lane; k < top; k += 32) wgt_t[k] = s[idx_t[k]] / (total + 1e-20f);
+}
+
+// One warp per token.  Shared per warp: s[n], c[n], g[groups].
+__global__ void seq_moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ corr, int n, int groups, int keep,
+                                     int top, int* __restrict__ idx, float* __restrict__ wgt, int T) {
+  extern __shared__ float route_smem[];
+  const int wpc = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * wpc + warp;
+  if (t >= T) return;
+  float* s = route_smem + (size_t)warp * (2 * n + groups);
+  route_token(z + (size_t)t * ldz, corr, n, groups, keep, top, idx + (size_t)t * top, wgt + (size_t)t * top, s, s + n, s + 2 * n, lane);
 }
 
 // Dot product of a weight row with a vector in shared memory (f32); the warp's lanes stride the row.
@@ -114,6 +118,26 @@ __device__ __forceinline__ float row_dot(const act_t* __restrict__ w, const floa
     for (int i = lane; i < n; i += 32) acc = fmaf(ld_act(w, i), x[i], acc);
   }
   return warp_sum(acc);
+}
+
+// Router of a few tokens in one launch: the logits W_router h_t (f32 accumulation of exact products; a warp per
+// router row) and the routing.  One CTA per token.  Shared: x[D], z[n], s[n], c[n], g[groups].
+template <typename act_t>
+__global__ void __launch_bounds__(256) seq_moe_route_fused_kernel(const act_t* __restrict__ h, int ldh, const act_t* __restrict__ wr,
+                                                                  const float* __restrict__ corr, int D, int n, int groups, int keep, int top,
+                                                                  int* __restrict__ idx, float* __restrict__ wgt, int vec) {
+  extern __shared__ float route_smem[];
+  float* x = route_smem;
+  float* z = x + D;
+  const int t = blockIdx.x, wpc = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) x[i] = ld_act(h, (size_t)t * ldh + i);
+  __syncthreads();
+  for (int r = warp; r < n; r += wpc) {
+    const float v = row_dot(wr + (size_t)r * D, x, D, lane, vec);
+    if (lane == 0) z[r] = v;
+  }
+  __syncthreads();
+  if (warp == 0) route_token(z, corr, n, groups, keep, top, idx + (size_t)t * top, wgt + (size_t)t * top, z + n, z + 2 * n, z + 3 * n, lane);
 }
 
 // mid[a, j] = silu(W_gate[e] h_t . ) * (W_up[e] h_t) for assignment a = t * top + k, e = idx[a].  grid (N, ff chunks).
@@ -254,6 +278,28 @@ extern "C" int b2l_seq_moe_route(const float* logits, int ld, const float* corre
 }
 
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+extern "C" int b2l_seq_moe_route_fused(const void* h, int ldh, const void* w_router, const float* correction, int D, int n, int groups,
+                                       int keep, int top, int* idx, float* weights, int T, int act_dtype, b2l_stream_t stream) {
+  B2L_CHECK_ARG(h && w_router && idx && weights, "b2l_seq_moe_route_fused: null pointer");
+  B2L_CHECK_ARG(T >= 0 && D > 0 && ldh >= D && n > 0 && top > 0 && top <= n && groups >= 1 && n % groups == 0 && keep >= 1 && keep <= groups,
+                "b2l_seq_moe_route_fused: bad size");
+  B2L_CHECK_ARG((long long)keep * (n / groups) >= top, "b2l_seq_moe_route_fused: the kept groups hold fewer than `top` experts");
+  if (T == 0) return 0;
+  const size_t smem = sizeof(float) * ((size_t)D + 3 * (size_t)n + groups);
+  B2L_CHECK_SUPPORTED(smem <= 200 * 1024, "b2l_seq_moe_route_fused: width %d and %d experts need %zu bytes of shared memory", D, n, smem);
+  static DynSmemCache cache[2];
+  B2L_SEQ_DISPATCH(act_dtype, {
+    constexpr int PER = 16 / sizeof(act_t);
+    const int vec = (D % PER == 0 && al16(w_router)) ? 1 : 0;
+    const int rc = ensure_dyn_smem(seq_moe_route_fused_kernel<act_t>, smem, cache[sizeof(act_t) == 2 ? 0 : 1]);
+    if (rc != 0) return rc;
+    seq_moe_route_fused_kernel<act_t><<<T, 256, smem, (cudaStream_t)stream>>>((const act_t*)h, ldh, (const act_t*)w_router, correction, D, n, groups,
+                                                                             keep, top, idx, weights, vec);
+  });
+  B2L_LAUNCH_CHECK("seq_moe_route_fused_kernel");
+  return 0;
+}
 
 extern "C" int b2l_seq_moe_experts_small(const void* h, int ldh, const void* w_gate_up, const void* w_down, const int* idx,
                                          const float* weights, void* mid, void* y, int ldy, int T, int D, int ff, int n_real,

@@ -548,10 +548,15 @@ class MoEFeedForward:
         lib, T, dev, D = S.lib(), ctx.T, h.device, h.shape[1]
         if torch.backends.cuda.matmul.allow_tf32:
             raise RuntimeError("router logits need true 32-bit products: torch.backends.cuda.matmul.allow_tf32 is on")
-        # f32 logits: bf16 activations and router weights are exact in f32, the product keeps its f32 accumulator
-        z = linear_f32(h, self.w_router)
         idx = torch.empty((T, self.top), dtype=torch.int32, device=dev)
         wgt = torch.empty((T, self.top), dtype=torch.float32, device=dev)
+        if T <= self.SMALL:        # a few tokens: the logits and the routing in one launch
+            S.check(lib.b2l_seq_moe_route_fused(_p(h), D, _p(self.w_router), _p(self.correction), D, self.n, self.groups, self.keep, self.top,
+                                                _p(idx), _p(wgt), T, ctx.act, ctx.stream), "b2l_seq_moe_route_fused")
+            self.last_idx = idx
+            return idx, wgt
+        # f32 logits: bf16 activations and router weights are exact in f32, the product keeps its f32 accumulator
+        z = linear_f32(h, self.w_router)
         S.check(lib.b2l_seq_moe_route(_p(z), self.n, _p(self.correction), self.n, self.groups, self.keep, self.top, _p(idx), _p(wgt), T,
                                       ctx.stream), "b2l_seq_moe_route")
         self.last_idx = idx

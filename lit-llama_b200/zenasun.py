@@ -171,18 +171,24 @@ class Zenasun:
         h2 = torch.empty((T, D), dtype=self.dtype, device=dev)
         if self.layers:
             self._norms(None, None, x, self.layers[0], h1, h2, T, ctx)
+        n = T if want is None else int(want.numel())
+        fuse_last = T == 1 and n == 1 and len(self.layers) > 0      # a single token: the last sum and the final norm in one launch
+        hn = torch.empty((n, D), dtype=self.dtype, device=dev) if n else None
         for i, layer in enumerate(self.layers):
             y1 = layer.mixer.forward(h1, ctx)
             y2 = layer.mlp.forward(h2, ctx) if layer.mlp is not None else None
-            self._norms(y1, y2, x, self.layers[i + 1] if i + 1 < len(self.layers) else None, h1, h2, T, ctx)
+            if i + 1 == len(self.layers) and fuse_last:
+                S.check(lib.b2l_seq_add_norm2(_p(y1), _p(y2), _p(x), _p(self.final_norm), _p(hn), None, None, 1.0, self.eps, None, 1, D, ctx.act,
+                                              ctx.stream), "b2l_seq_add_norm2")
+            else:
+                self._norms(y1, y2, x, self.layers[i + 1] if i + 1 < len(self.layers) else None, h1, h2, T, ctx)
             if self.capture_layers is not None:
                 self.capture_layers.append(x.clone())
-        n = T if want is None else int(want.numel())
         if n == 0:
             return torch.empty((0, self.vocab), dtype=torch.float32, device=dev)
-        hn = torch.empty((n, D), dtype=self.dtype, device=dev)
-        S.check(lib.b2l_seq_add_norm2(None, None, _p(x), _p(self.final_norm), _p(hn), None, None, 1.0, self.eps, _p(want), n, D, ctx.act,
-                                      ctx.stream), "b2l_seq_add_norm2")
+        if not fuse_last:
+            S.check(lib.b2l_seq_add_norm2(None, None, _p(x), _p(self.final_norm), _p(hn), None, None, 1.0, self.eps, _p(want), n, D, ctx.act,
+                                          ctx.stream), "b2l_seq_add_norm2")
         logits = linear_f32(hn, self.embed)
         if self.config.logit_softcap:
             S.check(lib.b2l_seq_softcap(_p(logits), logits.numel(), self.config.logit_softcap, ctx.stream), "b2l_seq_softcap")

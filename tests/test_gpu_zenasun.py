@@ -435,6 +435,10 @@ def test_router_and_experts(E, I, top, count, keep):
     assert int(clear.sum()) > T // 2
     assert torch.equal(idx.cpu().long()[clear], idx_want[clear])
     assert torch.allclose(wgt.cpu().double()[clear], w_want[clear], rtol=1e-5, atol=1e-7)
+    c3 = M.StepContext(3, ctx.meta, {}, torch.float32)                         # a few tokens: logits and routing in one launch
+    idx3, wgt3 = ff_layer.route(h[:3].to(DEV), c3)
+    assert torch.equal(idx3.cpu().long()[clear[:3]], idx_want[:3][clear[:3]])
+    assert torch.allclose(wgt3.cpu().double()[clear[:3]], w_want[:3][clear[:3]], rtol=1e-5, atol=1e-7)
     if I:
         assert int((idx_want >= E).sum()) > 0                                 # identity experts are exercised
     want = O.moe(h.double(), Wd, "mlp.", mlp)
