@@ -123,7 +123,7 @@ __device__ __forceinline__ float row_dot(const act_t* __restrict__ w, const floa
 // Router of a few tokens in one launch: the logits W_router h_t (f32 accumulation of exact products; a warp per
 // router row) and the routing.  One CTA per token.  Shared: x[D], z[n], s[n], c[n], g[groups].
 template <typename act_t>
-__global__ void __launch_bounds__(256) seq_moe_route_fused_kernel(const act_t* __restrict__ h, int ldh, const act_t* __restrict__ wr,
+__global__ void __launch_bounds__(1024) seq_moe_route_fused_kernel(const act_t* __restrict__ h, int ldh, const act_t* __restrict__ wr,
                                                                   const float* __restrict__ corr, int D, int n, int groups, int keep, int top,
                                                                   int* __restrict__ idx, float* __restrict__ wgt, int vec) {
   extern __shared__ float route_smem[];
@@ -294,7 +294,7 @@ extern "C" int b2l_seq_moe_route_fused(const void* h, int ldh, const void* w_rou
     const int vec = (D % PER == 0 && al16(w_router)) ? 1 : 0;
     const int rc = ensure_dyn_smem(seq_moe_route_fused_kernel<act_t>, smem, cache[sizeof(act_t) == 2 ? 0 : 1]);
     if (rc != 0) return rc;
-    seq_moe_route_fused_kernel<act_t><<<T, 256, smem, (cudaStream_t)stream>>>((const act_t*)h, ldh, (const act_t*)w_router, correction, D, n, groups,
+    seq_moe_route_fused_kernel<act_t><<<T, n >= 32 ? 1024 : 32 * ((n + 3) / 4 * 4 > 8 ? (n + 3) / 4 * 4 : 8), smem, (cudaStream_t)stream>>>((const act_t*)h, ldh, (const act_t*)w_router, correction, D, n, groups,
                                                                              keep, top, idx, weights, vec);
   });
   B2L_LAUNCH_CHECK("seq_moe_route_fused_kernel");
