@@ -153,20 +153,54 @@ __global__ void __launch_bounds__(LAT_THREADS, VI <= 4 ? 3 : 1) seq_latent_atten
   for (int jt = j_begin; jt < j_end; jt += LAT_BN) {
     __syncthreads();                                                // the previous tile is consumed (and qs is written)
     const int nk = min(LAT_BN, j_end - jt);
-    for (int j = warp; j < LAT_BN; j += nw) {                       // a warp per key row, lanes along the row
-      const bool ok = j < nk;
-      const act_t* pa = key_a + (size_t)(jt + j) * a.ldka;
-      const act_t* pb = key_b + (size_t)(jt + j) * a.ldkb;
+    {
+      // a warp loads LAT_BN / 8 key rows, lanes along the rows; the loads of all its rows are issued together, before
+      // the first store, so a tile costs a few memory latencies instead of one per row
+      constexpr int KPW = LAT_BN / (LAT_THREADS / 32);
+      const act_t* pa[KPW];
+      const act_t* pb[KPW];
+      bool ok[KPW];
+#pragma unroll
+      for (int u = 0; u < KPW; ++u) {
+        const int j = warp + u * (LAT_THREADS / 32);
+        ok[u] = j < nk;
+        pa[u] = key_a + (size_t)(jt + (ok[u] ? j : 0)) * a.ldka;
+        pb[u] = key_b + (size_t)(jt + (ok[u] ? j : 0)) * a.ldkb;
+      }
 #pragma unroll 4
-      for (int d = lane; d < a.n_a; d += 32) kT[(size_t)d * LAT_LDK + j] = ok ? ld_act(pa, d) : 0.f;
+      for (int d = lane; d < a.n_a; d += 32) {
+        float v[KPW];
+#pragma unroll
+        for (int u = 0; u < KPW; ++u) v[u] = ld_act(pa[u], d);
+#pragma unroll
+        for (int u = 0; u < KPW; ++u) kT[(size_t)d * LAT_LDK + warp + u * (LAT_THREADS / 32)] = ok[u] ? v[u] : 0.f;
+      }
 #pragma unroll 2
-      for (int d = lane; d < a.n_b; d += 32) kT[(size_t)(a.n_a + d) * LAT_LDK + j] = ok ? ld_act(pb, d) : 0.f;
+      for (int d = lane; d < a.n_b; d += 32) {
+        float v[KPW];
+#pragma unroll
+        for (int u = 0; u < KPW; ++u) v[u] = ld_act(pb[u], d);
+#pragma unroll
+        for (int u = 0; u < KPW; ++u) kT[(size_t)(a.n_a + d) * LAT_LDK + warp + u * (LAT_THREADS / 32)] = ok[u] ? v[u] : 0.f;
+      }
     }
     __syncthreads();
     if (jt > warp_lim) continue;                                    // every key of the tile lies after this warp's rows
-    float s[LAT_RW] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 2
-    for (int d = s0; d < Kp; d += 4) {
+    float s[LAT_RW] = {0.f, 0.f, 0.f, 0.f}, s2[LAT_RW] = {0.f, 0.f, 0.f, 0.f};     // two chains per row: the FMAs of one hide the other's latency
+    int d = s0;
+    for (; d + 8 <= Kp; d += 8) {
+      float k[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) k[u] = kT[(size_t)(d + u) * LAT_LDK + lane];
+#pragma unroll
+      for (int r = 0; r < LAT_RW; ++r) {
+        const float4 qa = *reinterpret_cast<const float4*>(qw + (size_t)r * Qp + (d - s0));
+        const float4 qb = *reinterpret_cast<const float4*>(qw + (size_t)r * Qp + (d - s0) + 4);
+        s[r] = fmaf(qa.x, k[0], fmaf(qa.y, k[1], fmaf(qa.z, k[2], fmaf(qa.w, k[3], s[r]))));
+        s2[r] = fmaf(qb.x, k[4], fmaf(qb.y, k[5], fmaf(qb.z, k[6], fmaf(qb.w, k[7], s2[r]))));
+      }
+    }
+    for (; d < Kp; d += 4) {
       const float k0 = kT[(size_t)d * LAT_LDK + lane], k1 = kT[(size_t)(d + 1) * LAT_LDK + lane];
       const float k2 = kT[(size_t)(d + 2) * LAT_LDK + lane], k3 = kT[(size_t)(d + 3) * LAT_LDK + lane];
 #pragma unroll
@@ -175,6 +209,8 @@ __global__ void __launch_bounds__(LAT_THREADS, VI <= 4 ? 3 : 1) seq_latent_atten
         s[r] = fmaf(q4.x, k0, fmaf(q4.y, k1, fmaf(q4.z, k2, fmaf(q4.w, k3, s[r]))));
       }
     }
+#pragma unroll
+    for (int r = 0; r < LAT_RW; ++r) s[r] += s2[r];
     const int j = jt + lane;
 #pragma unroll
     for (int r = 0; r < LAT_RW; ++r) {
