@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(LAT_THREADS, VI <= 4 ? 3 : 1) seq_latent_atten
   float* qs = kT + (size_t)Kp * LAT_LDK;
   float* ps = qs + (size_t)rows_cta * Qp;
   const int slot = a.meta[0], pos0 = a.meta[1];
-  const int row0 = blockIdx.x * rows_cta;
+  const int row0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * rows_cta;      // the rows with the most keys start first
   const act_t* key_a = reinterpret_cast<const act_t*>(a.key_a) + (size_t)slot * a.slot_stride_a + (size_t)group * a.hska;
   const act_t* key_b = reinterpret_cast<const act_t*>(a.key_b) + (size_t)slot * a.slot_stride_b;
 

@@ -407,9 +407,9 @@ class LatentAttention:
         n_keys = self.max_positions if ctx.pos_hint is None else min(self.max_positions, ctx.pos_hint + T)
         warps = S.lib().b2l_seq_latent_attention_warps(T, hpg)
         ctas = -(-T * hpg // (4 * warps)) * (self.H // hpg)
-        if ctas >= 148:
+        if ctas >= 444:                       # a full wave of three CTAs per SM
             return 1
-        return max(1, min(-(-296 // ctas), -(-n_keys // 32)))
+        return max(1, min(-(-444 // ctas), -(-n_keys // 32)))
 
     def _attend(self, ctx: StepContext, out: torch.Tensor, vdim: int, splits: int, **kw) -> None:
         work = torch.empty((splits, ctx.T * self.H, vdim + 2), dtype=torch.float32, device=out.device) if splits > 1 else None
