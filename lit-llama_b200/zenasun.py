@@ -144,7 +144,9 @@ class Zenasun:
         seen, n = set(), 0
         for layer in self.layers:
             for obj in (layer.mixer, layer.mlp):
-                for v in vars(obj).values() if obj is not None else []:
+                for k, v in vars(obj).items() if obj is not None else []:
+                    if k == "w_expand":            # a second arrangement of W_uk and W_uv, not more parameters
+                        continue
                     if isinstance(v, torch.Tensor) and v.is_floating_point() and v.dim() >= 2 and v.data_ptr() not in seen:
                         seen.add(v.data_ptr())
                         n += v.numel()
